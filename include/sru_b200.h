@@ -1,0 +1,152 @@
+/*
+ * sru_b200 -- C ABI of the B200 (sm_100a) SRU hot path: the light-recurrence scan
+ * (forward / backward) and the projection GEMM U = x * W.
+ *
+ * Plain pointers and sizes only; every pointer is a DEVICE pointer unless said
+ * otherwise; every call is asynchronous on the given CUDA stream (a cudaStream_t
+ * passed as void*).  Return value: 0 on success, a negative SRU_ERR_* code
+ * otherwise; sru_b200_last_error() gives the message of the calling thread's last
+ * failure.  No exception crosses this boundary and there is no CPU fallback.
+ *
+ * Tensor layouts are the reference's (asappresearch/sru v2.6.0):
+ *   u, grad_u      (L, B, dirs, d, k)   gate index innermost
+ *                  (sru/csrc/sru_cuda_kernel.cu:54,218; sru/ops.py:176)
+ *   x, h, grad_h, grad_x, c_hist   (L, B, dirs*d)
+ *   weight_c, bias, grad_weight_c, grad_bias   (2, dirs, d)
+ *                  (sru_cuda_kernel.cu:47-51,212-216; ops.py:183-185)
+ *   custom V / its gradient (is_custom != 0)   (L, B, dirs, d, 2)
+ *   c_init, mask_c, c_last, grad_last, grad_init   (B, dirs*d)
+ *   mask_pad       (L, B) bytes, non-zero = padded position
+ *                  (sru_cuda_kernel.cu:56,61)
+ *
+ * Element types.  `dtype` is the storage type of the large per-time-step tensors
+ * (u, x, h, grad_h, grad_u, grad_x, custom V); `c_dtype` is the storage type of
+ * c_hist (the same as dtype, or SRU_F32).  The small per-column tensors
+ * (weight_c when not custom, bias, c_init, mask_c, c_last, grad_last,
+ * grad_weight_c when not custom, grad_bias, grad_init) are float, or double when
+ * dtype == SRU_F64.  Arithmetic is float (double for SRU_F64).
+ */
+#ifndef SRU_B200_H_
+#define SRU_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { SRU_F32 = 0, SRU_F16 = 1, SRU_BF16 = 2, SRU_F64 = 3 };
+
+enum {
+    SRU_OK = 0,
+    SRU_ERR_BAD_ARG = -1,      /* null pointer, bad size, unknown enum value        */
+    SRU_ERR_UNSUPPORTED = -2,  /* combination not implemented (message says which)  */
+    SRU_ERR_WORKSPACE = -3,    /* workspace missing or too small                    */
+    SRU_ERR_CUDA = -4,         /* a CUDA runtime / driver call failed               */
+    SRU_ERR_DEVICE = -5        /* a kernel reported a timed-out wait (see below)    */
+};
+
+/* Library version, major*10000 + minor*100 + patch. */
+int sru_b200_version(void);
+
+/* Message of the calling thread's most recent failure ("" if none). */
+const char *sru_b200_last_error(void);
+
+/*
+ * Synchronises `stream` and returns SRU_ERR_DEVICE if any kernel since the last
+ * call gave up a bounded wait (an mbarrier that never completed); the flag is
+ * cleared.  Kernels never spin without a limit, so a lost copy shows up here as
+ * an error code instead of a hang.
+ */
+int sru_b200_check_device_error(void *stream);
+
+/*
+ * Forward scan.  Replaces the four forward launchers of the reference,
+ * sru_cuda_forward_simple / sru_cuda_bi_forward_simple / sru_cuda_forward /
+ * sru_cuda_bi_forward (sru/csrc/sru_cuda_kernel.cu:827-860, :911-944, :995-1036,
+ * :1039-1080), and the glue around them in sru/cuda_functional.py:38-153:
+ * x*scale_x (:73-78) is applied in the kernel, and last_hidden (:146-152) is
+ * written to c_last by the kernel.
+ *
+ *   h        out, every element written (0 at padded positions)
+ *   c_hist   out, may be NULL (inference: the backward pass is not needed)
+ *   c_last   out, may be NULL; final state per column: c[L-1] for direction 0,
+ *            c[0] for direction 1
+ *   x        used only when skip_type == 1 (may be NULL otherwise)
+ *   bias     may be NULL: the bias has already been added to u by the producer
+ *   c_init   may be NULL (zeros); mask_c, mask_pad may be NULL
+ *   dirs     1 or 2; k 3 or 4; activation_type 0 (identity) or 1 (tanh)
+ *   skip_type 0 none, 1 x (k == 3), 2 u[...,3] (k == 4)
+ *   scale_x  multiplies x when skip_type == 1 (pass 1.0 for none)
+ */
+int sru_b200_scan_forward(
+    void *h, void *c_hist, void *c_last,
+    const void *u, const void *x, const void *weight_c, const void *bias,
+    const void *c_init, const void *mask_c, const uint8_t *mask_pad,
+    int64_t length, int64_t batch, int64_t hidden, int dirs, int k,
+    int activation_type, int skip_type, int is_custom, double scale_x,
+    int dtype, int c_dtype, void *stream);
+
+/*
+ * Bytes of scratch the backward scan needs for the same problem (partials of the
+ * batch reduction of grad_weight_c / grad_bias).  Never more than
+ * 32 * batch * dirs * hidden bytes.
+ */
+size_t sru_b200_scan_backward_workspace_bytes(
+    int64_t length, int64_t batch, int64_t hidden, int dirs, int k, int dtype);
+
+/*
+ * Backward scan.  Replaces sru_cuda_backward_simple / sru_cuda_bi_backward_simple /
+ * sru_cuda_backward / sru_cuda_bi_backward (sru_cuda_kernel.cu:863-908, :947-992,
+ * :1083-1136, :1139-1192) and the host tail of sru/cuda_functional.py:253-260:
+ * grad_x is multiplied by scale_x in the kernel and grad_weight_c / grad_bias are
+ * reduced over the batch on the device, deterministically (fixed summation order,
+ * no atomics), into (2, dirs, d).
+ *
+ *   grad_u     out, every element written (0 at padded positions)
+ *   grad_x     out when skip_type == 1 (NULL otherwise)
+ *   grad_wc    out: (2, dirs, d), or the per-step (L, B, dirs, d, 2) when is_custom
+ *   grad_bias  out (2, dirs, d);  grad_init out (B, dirs*d)
+ *   c_hist     the forward's saved states; grad_last may be NULL (zeros)
+ *   workspace  device scratch of at least ..._workspace_bytes(); contents are
+ *              undefined afterwards; calls sharing one workspace must be
+ *              stream-ordered
+ */
+int sru_b200_scan_backward(
+    void *grad_u, void *grad_x, void *grad_wc, void *grad_bias, void *grad_init,
+    const void *u, const void *x, const void *weight_c, const void *bias,
+    const void *c_init, const void *mask_c, const uint8_t *mask_pad,
+    const void *c_hist, const void *grad_h, const void *grad_last,
+    int64_t length, int64_t batch, int64_t hidden, int dirs, int k,
+    int activation_type, int skip_type, int is_custom, double scale_x,
+    int dtype, int c_dtype, void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * Dense contraction on the tcgen05 tensor cores, the replacement for the three
+ * library GEMMs around the scan: U = x * W of SRUCell.compute_U
+ * (sru/modules.py:363-378) and, in backward, grad_x = grad_U * W^T and
+ * grad_W = x^T * grad_U that autograd derives from it.
+ *
+ *   C[M,N] (row-major, leading dimension ldc) = op(A) * op(B) (+ col_bias)
+ *   op(A) is M x K: A stored row-major (M,K) when trans_a == 0, or (K,M) when 1
+ *   op(B) is K x N: B stored row-major (K,N) when trans_b == 0, or (N,K) when 1
+ *   ab_dtype  SRU_BF16 or SRU_F16 (fp32 accumulation in tensor memory)
+ *   c_dtype   SRU_BF16, SRU_F16 or SRU_F32
+ *   col_bias  float[N] added to every row in the epilogue, or NULL.  With the gate
+ *             bias of the SRU scattered to the gate-innermost columns
+ *             ((dir*d+j)*k+1 -> bias[0,dir,j], (dir*d+j)*k+2 -> bias[1,dir,j])
+ *             this folds `bias` into U, and the scan is then called with bias=NULL.
+ *   accumulate  non-zero: C += result (C read in the epilogue)
+ * Leading dimensions are in elements and must make every row start 16-byte aligned.
+ */
+int sru_b200_gemm(
+    void *c, const void *a, const void *b, const float *col_bias,
+    int64_t m, int64_t n, int64_t k_dim,
+    int64_t lda, int64_t ldb, int64_t ldc,
+    int trans_a, int trans_b, int ab_dtype, int c_dtype, int accumulate, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SRU_B200_H_ */

@@ -1,0 +1,84 @@
+"""ctypes access to libsru_b200.so (the C ABI of include/sru_b200.h).
+
+There is no fallback: if the library is missing or fails to load, every operator raises.
+"""
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libsru_b200.so")
+TORCH_LIB_PATH = os.path.join(_HERE, "lib", "libsru_b200_torch.so")
+
+SRU_F32, SRU_F16, SRU_BF16, SRU_F64 = 0, 1, 2, 3
+DTYPE_CODE = {torch.float32: SRU_F32, torch.float16: SRU_F16, torch.bfloat16: SRU_BF16,
+              torch.float64: SRU_F64}
+
+_lib = None
+_torch_ops_loaded = False
+
+_vp = ctypes.c_void_p
+_i64 = ctypes.c_int64
+_int = ctypes.c_int
+
+
+class SruB200Error(RuntimeError):
+    pass
+
+
+def lib():
+    """The loaded C-ABI library.  Raises if it has not been built (python -m sru_b200.build)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise SruB200Error(
+                "libsru_b200.so not found at %s: build it with `python -m sru_b200.build`; "
+                "this package has no CPU or PyTorch fallback" % LIB_PATH)
+        l = ctypes.CDLL(LIB_PATH)
+        l.sru_b200_version.restype = _int
+        l.sru_b200_last_error.restype = ctypes.c_char_p
+        l.sru_b200_check_device_error.restype = _int
+        l.sru_b200_check_device_error.argtypes = [_vp]
+        l.sru_b200_scan_forward.restype = _int
+        l.sru_b200_scan_forward.argtypes = [_vp] * 10 + [_i64, _i64, _i64, _int, _int, _int, _int, _int,
+                                                         ctypes.c_double, _int, _int, _vp]
+        l.sru_b200_scan_backward_workspace_bytes.restype = ctypes.c_size_t
+        l.sru_b200_scan_backward_workspace_bytes.argtypes = [_i64, _i64, _i64, _int, _int, _int]
+        l.sru_b200_scan_backward.restype = _int
+        l.sru_b200_scan_backward.argtypes = [_vp] * 15 + [_i64, _i64, _i64, _int, _int, _int, _int, _int,
+                                                          ctypes.c_double, _int, _int, _vp, ctypes.c_size_t, _vp]
+        l.sru_b200_gemm.restype = _int
+        l.sru_b200_gemm.argtypes = [_vp] * 4 + [_i64] * 6 + [_int] * 5 + [_vp]
+        _lib = l
+    return _lib
+
+
+def load_torch_ops():
+    """Registers torch.ops.sru_cuda.* (the reference's operator names) from the binding library."""
+    global _torch_ops_loaded
+    if not _torch_ops_loaded:
+        if not os.path.exists(TORCH_LIB_PATH):
+            raise SruB200Error("libsru_b200_torch.so not found at %s: run `python -m sru_b200.build`"
+                               % TORCH_LIB_PATH)
+        lib()
+        torch.ops.load_library(TORCH_LIB_PATH)
+        _torch_ops_loaded = True
+
+
+def check(rc):
+    if rc != 0:
+        msg = lib().sru_b200_last_error().decode("utf-8", "replace")
+        raise SruB200Error("sru_b200 call failed (%d): %s" % (rc, msg))
+
+
+def ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def current_stream_ptr(device=None):
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def check_device_error(device=None):
+    check(lib().sru_b200_check_device_error(current_stream_ptr(device)))

@@ -1,0 +1,271 @@
+"""Operator layer of the SRU hot path on B200: the light-recurrence scan through the C ABI.
+
+Mirrors the reference's operator interface for this path:
+
+* ``elementwise_recurrence_gpu``  -- sru/ops.py:97-142 (same arguments, same return value)
+* ``ElementwiseRecurrence``       -- sru/cuda_functional.py:156-261 (autograd glue)
+* ``elementwise_recurrence_forward`` -- sru/cuda_functional.py:37-153 (returns h, last_hidden, c)
+
+Differences, all inside the boundary: the kernels read U / x / grad_h in their storage
+dtype and compute in fp32 registers (no fp32 copies of U); ``x * scale_x``, the
+bidirectional ``last_hidden`` gather, ``grad_x *= scale_x`` and the batch reduction of
+``grad_weight_c`` / ``grad_bias`` happen inside the kernels; outputs are not memset.
+There is no CPU path here: tensors must be CUDA tensors and the native library must load.
+"""
+from typing import List, Optional, Tuple
+
+import torch
+from torch import Tensor
+from torch.autograd import Function
+
+from . import _lib
+
+# How a 16-bit U (from an autocast GEMM) is handled.
+#   "native":    scan reads/writes the 16-bit storage dtype directly, h comes back in that dtype.
+#   "reference": U and x are first cast to fp32 exactly as sru/ops.py:116-127 does (fp16 when
+#                amp_recurrence_fp16 and U is fp16), h comes back in that cast dtype.
+_amp_mode = "native"
+# Storage of the saved state history c (L,B,D) when U is 16-bit: "float32" or "storage".
+_c_hist_dtype = "float32"
+
+
+def set_amp_mode(mode: str) -> None:
+    global _amp_mode
+    if mode not in ("native", "reference"):
+        raise ValueError("amp mode must be 'native' or 'reference'")
+    _amp_mode = mode
+
+
+def get_amp_mode() -> str:
+    return _amp_mode
+
+
+def set_c_hist_dtype(kind: str) -> None:
+    global _c_hist_dtype
+    if kind not in ("float32", "storage"):
+        raise ValueError("c_hist dtype must be 'float32' or 'storage'")
+    _c_hist_dtype = kind
+
+
+def _small_dtype(storage: torch.dtype) -> torch.dtype:
+    return torch.float64 if storage == torch.float64 else torch.float32
+
+
+def _c_dtype_for(storage: torch.dtype) -> torch.dtype:
+    if storage in (torch.float16, torch.bfloat16) and _c_hist_dtype == "float32":
+        return torch.float32
+    return storage
+
+
+def _require_cuda(t: Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise _lib.SruB200Error("%s must be a CUDA tensor: sru_b200 has no CPU path" % name)
+
+
+def _geometry(u: Tensor, x: Tensor, d: int, bidirectional: bool, has_skip_term: bool, weight_c: Tensor):
+    dirs = 2 if bidirectional else 1
+    length = x.size(0) if x.dim() == 3 else 1
+    batch = x.size(-2)
+    k = u.size(-1) // d // dirs
+    skip_type = 0 if not has_skip_term else (1 if k == 3 else 2)
+    is_custom = 1 if weight_c.dim() > 1 else 0
+    return length, batch, dirs, k, skip_type, is_custom
+
+
+def scan_forward(u: Tensor, x: Optional[Tensor], weight_c: Tensor, bias: Optional[Tensor],
+                 c_init: Optional[Tensor], mask_c: Optional[Tensor], mask_pad: Optional[Tensor],
+                 length: int, batch: int, d: int, dirs: int, k: int, activation_type: int,
+                 skip_type: int, is_custom: int, scale_x: float, need_c_hist: bool = True,
+                 c_dtype: Optional[torch.dtype] = None) -> Tuple[Tensor, Optional[Tensor], Tensor]:
+    """Raw forward call.  u is (L,B,D*k) in the storage dtype; returns h, c_hist (or None), c_last."""
+    _require_cuda(u, "U")
+    st = u.dtype
+    sm = _small_dtype(st)
+    D = d * dirs
+    if c_dtype is None:
+        c_dtype = _c_dtype_for(st)
+    h = torch.empty(length, batch, D, dtype=st, device=u.device)
+    c_hist = torch.empty(length, batch, D, dtype=c_dtype, device=u.device) if need_c_hist else None
+    c_last = torch.empty(batch, D, dtype=sm, device=u.device)
+    if length == 0 or batch == 0:
+        if c_init is not None:
+            c_last.copy_(c_init.reshape(batch, D))
+        else:
+            c_last.zero_()
+        return h, c_hist, c_last
+    with torch.cuda.device(u.device):
+        _lib.check(_lib.lib().sru_b200_scan_forward(
+            _lib.ptr(h), _lib.ptr(c_hist), _lib.ptr(c_last), _lib.ptr(u), _lib.ptr(x),
+            _lib.ptr(weight_c), _lib.ptr(bias), _lib.ptr(c_init), _lib.ptr(mask_c), _lib.ptr(mask_pad),
+            length, batch, d, dirs, k, activation_type, skip_type, is_custom, float(scale_x),
+            _lib.DTYPE_CODE[st], _lib.DTYPE_CODE[c_dtype], _lib.current_stream_ptr(u.device)))
+    return h, c_hist, c_last
+
+
+def scan_backward(u, x, weight_c, bias, c_init, mask_c, mask_pad, c_hist, grad_h, grad_last,
+                  length, batch, d, dirs, k, activation_type, skip_type, is_custom, scale_x):
+    """Raw backward call.  Returns grad_u, grad_x (or None), grad_wc, grad_bias (2*D), grad_init."""
+    st = u.dtype
+    sm = _small_dtype(st)
+    D = d * dirs
+    dev = u.device
+    grad_u = torch.empty_like(u)
+    grad_x = torch.empty(length, batch, D, dtype=st, device=dev) if skip_type == 1 else None
+    if is_custom:
+        grad_wc = torch.empty(length, batch, D * 2, dtype=st, device=dev)
+    else:
+        grad_wc = torch.empty(2 * D, dtype=sm, device=dev)
+    grad_bias = torch.empty(2 * D, dtype=sm, device=dev)
+    grad_init = torch.empty(batch, D, dtype=sm, device=dev)
+    if length == 0 or batch == 0:
+        grad_wc.zero_(); grad_bias.zero_()
+        if grad_last is not None:
+            grad_init.copy_(grad_last)
+        else:
+            grad_init.zero_()
+        return grad_u, grad_x, grad_wc, grad_bias, grad_init
+    L = _lib.lib()
+    code = _lib.DTYPE_CODE[st]
+    nbytes = L.sru_b200_scan_backward_workspace_bytes(length, batch, d, dirs, k, code)
+    workspace = torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(L.sru_b200_scan_backward(
+            _lib.ptr(grad_u), _lib.ptr(grad_x), _lib.ptr(grad_wc), _lib.ptr(grad_bias), _lib.ptr(grad_init),
+            _lib.ptr(u), _lib.ptr(x), _lib.ptr(weight_c), _lib.ptr(bias), _lib.ptr(c_init),
+            _lib.ptr(mask_c), _lib.ptr(mask_pad), _lib.ptr(c_hist), _lib.ptr(grad_h), _lib.ptr(grad_last),
+            length, batch, d, dirs, k, activation_type, skip_type, is_custom, float(scale_x),
+            code, _lib.DTYPE_CODE[c_hist.dtype], _lib.ptr(workspace), workspace.numel(),
+            _lib.current_stream_ptr(dev)))
+    return grad_u, grad_x, grad_wc, grad_bias, grad_init
+
+
+def _prep_small(t: Optional[Tensor], dtype: torch.dtype) -> Optional[Tensor]:
+    if t is None:
+        return None
+    return t.detach().to(dtype).contiguous()
+
+
+class ElementwiseRecurrence(Function):
+    """Autograd function of the scan; argument order of sru/cuda_functional.py:158-169."""
+
+    @staticmethod
+    def forward(ctx, u, x, weight_c, bias, init, activation_type, d_out, bidirectional,
+                has_skip_term, scale_x, mask_c=None, mask_pad=None):
+        length, batch, dirs, k, skip_type, is_custom = _geometry(u, x, d_out, bidirectional,
+                                                                 has_skip_term, weight_c)
+        st = u.dtype
+        sm = _small_dtype(st)
+        D = d_out * dirs
+        u_c = u.detach().contiguous()
+        x_c = x.detach().to(st).contiguous() if skip_type == 1 else None
+        wc_c = weight_c.detach().to(st if is_custom else sm).contiguous()
+        bias_c = _prep_small(bias, sm)
+        init_c = _prep_small(init, sm)
+        mask_c_c = _prep_small(mask_c, sm)
+        pad_c = mask_pad.bool().contiguous() if mask_pad is not None else None
+        scale = 1.0 if scale_x is None else float(scale_x.reshape(-1)[0])
+        need_hist = any(ctx.needs_input_grad[:5])
+        h, c_hist, c_last = scan_forward(u_c.view(length, batch, D * k), x_c, wc_c, bias_c, init_c,
+                                         mask_c_c, pad_c, length, batch, d_out, dirs, k,
+                                         activation_type, skip_type, is_custom, scale, need_hist)
+        ctx.meta = (length, batch, d_out, dirs, k, activation_type, skip_type, is_custom, scale)
+        ctx.shapes = (u.shape, x.shape, x.dtype, weight_c.shape, weight_c.dtype, bias.dtype,
+                      init.shape, init.dtype)
+        ctx.save_for_backward(u_c, x_c, wc_c, bias_c, init_c, mask_c_c, pad_c, c_hist)
+        if x.dim() == 2:
+            h = h.squeeze(0)
+        return h, c_last.to(init.dtype) if init.dtype != c_last.dtype else c_last
+
+    @staticmethod
+    def backward(ctx, grad_h, grad_last):
+        u, x, wc, bias, init, mask_c, pad, c_hist = ctx.saved_tensors
+        length, batch, d, dirs, k, act, skip_type, is_custom, scale = ctx.meta
+        u_shape, x_shape, x_dtype, wc_shape, wc_dtype, bias_dtype, init_shape, init_dtype = ctx.shapes
+        D = d * dirs
+        st = u.dtype
+        sm = _small_dtype(st)
+        gh = grad_h.to(st).contiguous().view(length, batch, D)
+        gl = _prep_small(grad_last, sm)
+        grad_u, grad_x, grad_wc, grad_bias, grad_init = scan_backward(
+            u.view(length, batch, D * k), x, wc, bias, init, mask_c, pad, c_hist, gh, gl,
+            length, batch, d, dirs, k, act, skip_type, is_custom, scale)
+        grad_u = grad_u.view(u_shape)
+        if grad_x is not None:
+            grad_x = grad_x.view(x_shape).to(x_dtype)
+        grad_wc = grad_wc.view(wc_shape).to(wc_dtype)
+        return (grad_u, grad_x, grad_wc, grad_bias.to(bias_dtype), grad_init.view(init_shape).to(init_dtype),
+                None, None, None, None, None, None, None)
+
+
+def elementwise_recurrence_forward(u: Tensor, x: Tensor, weight_c: Tensor, bias: Tensor, init: Tensor,
+                                   activation_type: int, d_out: int, bidirectional: bool,
+                                   has_skip_term: bool, scale_x: Optional[Tensor] = None,
+                                   mask_c: Optional[Tensor] = None,
+                                   mask_pad: Optional[Tensor] = None) -> Tuple[Tensor, Tensor, Tensor]:
+    """No-grad forward returning (h, last_hidden, c) as sru/cuda_functional.py:37-153 does."""
+    length, batch, dirs, k, skip_type, is_custom = _geometry(u, x, d_out, bidirectional,
+                                                             has_skip_term, weight_c)
+    st = u.dtype
+    sm = _small_dtype(st)
+    D = d_out * dirs
+    scale = 1.0 if scale_x is None else float(scale_x.reshape(-1)[0])
+    h, c_hist, c_last = scan_forward(
+        u.detach().contiguous().view(length, batch, D * k),
+        x.detach().to(st).contiguous() if skip_type == 1 else None,
+        weight_c.detach().to(st if is_custom else sm).contiguous(), _prep_small(bias, sm),
+        _prep_small(init, sm), _prep_small(mask_c, sm),
+        mask_pad.bool().contiguous() if mask_pad is not None else None,
+        length, batch, d_out, dirs, k, activation_type, skip_type, is_custom, scale, True)
+    if x.dim() == 2:
+        h, c_hist = h.squeeze(0), c_hist.squeeze(0)
+    return h, c_last, c_hist
+
+
+def elementwise_recurrence_gpu(U: Tensor, x: Tensor, weight_c: Tensor, bias: Tensor, c_init: Tensor,
+                               activation_type: int, hidden_size: int, bidirectional: bool,
+                               has_skip_term: bool, scale_x: Optional[Tensor] = None,
+                               dropout_mask_c: Optional[Tensor] = None,
+                               mask_pad: Optional[Tensor] = None,
+                               amp_recurrence_fp16: bool = False) -> List[Tensor]:
+    """Elementwise recurrence of SRU on the GPU; signature of sru/ops.py:98-110.
+
+    Returns ``[h, last_c]``.  In "reference" amp mode the casts of sru/ops.py:116-127 are
+    applied first, so dtypes of the results equal the reference's; in "native" mode (default)
+    a 16-bit U is consumed as it is and h has U's dtype, last_c has c_init's dtype.
+    """
+    _require_cuda(U, "U")
+    if _amp_mode == "reference":
+        if amp_recurrence_fp16 and U.dtype == torch.float16:
+            cast = torch.Tensor.half
+        else:
+            cast = torch.Tensor.float
+        U, x, c_init = cast(U), cast(x), cast(c_init)
+    if not torch.is_grad_enabled() or not any(
+            t is not None and t.requires_grad for t in (U, x, weight_c, bias, c_init)):
+        h, c_last, _ = _forward_nograd(U, x, weight_c, bias, c_init, activation_type, hidden_size,
+                                       bidirectional, has_skip_term, scale_x, dropout_mask_c, mask_pad)
+        return [h, c_last.to(c_init.dtype)]
+    return list(ElementwiseRecurrence.apply(U, x, weight_c, bias, c_init, activation_type, hidden_size,
+                                            bidirectional, has_skip_term, scale_x, dropout_mask_c,
+                                            mask_pad))
+
+
+def _forward_nograd(U, x, weight_c, bias, c_init, activation_type, hidden_size, bidirectional,
+                    has_skip_term, scale_x, mask_c, mask_pad):
+    """Inference: no state history is written (5 instead of 6 elements of traffic per column-step)."""
+    length, batch, dirs, k, skip_type, is_custom = _geometry(U, x, hidden_size, bidirectional,
+                                                             has_skip_term, weight_c)
+    st = U.dtype
+    sm = _small_dtype(st)
+    D = hidden_size * dirs
+    scale = 1.0 if scale_x is None else float(scale_x.reshape(-1)[0])
+    h, _, c_last = scan_forward(
+        U.detach().contiguous().view(length, batch, D * k),
+        x.detach().to(st).contiguous() if skip_type == 1 else None,
+        weight_c.detach().to(st if is_custom else sm).contiguous(), _prep_small(bias, sm),
+        _prep_small(c_init, sm), _prep_small(mask_c, sm),
+        mask_pad.bool().contiguous() if mask_pad is not None else None,
+        length, batch, hidden_size, dirs, k, activation_type, skip_type, is_custom, scale, False)
+    if x.dim() == 2:
+        h = h.squeeze(0)
+    return h, c_last, None

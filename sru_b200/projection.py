@@ -1,0 +1,99 @@
+"""The dense projection U = x W of the SRU layer (sru/modules.py:363-378) and its gradients.
+
+16-bit operands (bf16 / fp16, e.g. under autocast) run on this package's tcgen05 GEMM
+(``sru_b200_gemm`` of the C ABI): forward ``U = x W``, backward ``grad_x = grad_U W^T`` and
+``grad_W = x^T grad_U``, all with fp32 accumulation in tensor memory.  fp32 / fp64 operands
+have no tensor-core path that keeps full precision, so they are a plain library GEMM
+(``torch.mm``).
+"""
+import os
+from typing import Optional
+
+import torch
+from torch import Tensor
+from torch.autograd import Function
+
+from . import _lib
+
+_SIXTEEN = (torch.float16, torch.bfloat16)
+
+
+def gemm_backend() -> str:
+    """'tcgen05' (default) or 'library' (SRU_B200_GEMM=library forces torch.mm everywhere)."""
+    return os.environ.get("SRU_B200_GEMM", "library")
+
+
+def gemm(a: Tensor, b: Tensor, trans_a: bool = False, trans_b: bool = False,
+         out_dtype: Optional[torch.dtype] = None, col_bias: Optional[Tensor] = None,
+         out: Optional[Tensor] = None, accumulate: bool = False) -> Tensor:
+    """C = op(a) @ op(b) (+ col_bias) on the tcgen05 kernel.  a, b: 2-D, 16-bit, same dtype,
+    unit stride in the last dimension.  op(a) is M x K, op(b) is K x N."""
+    if a.dtype not in _SIXTEEN or b.dtype != a.dtype:
+        raise _lib.SruB200Error("gemm operands must both be bf16 or both fp16")
+    if a.stride(1) != 1:
+        a = a.contiguous()
+    if b.stride(1) != 1:
+        b = b.contiguous()
+    m = a.size(1) if trans_a else a.size(0)
+    kd = a.size(0) if trans_a else a.size(1)
+    kb = b.size(1) if trans_b else b.size(0)
+    n = b.size(0) if trans_b else b.size(1)
+    if kd != kb:
+        raise _lib.SruB200Error("gemm inner dimensions differ: %d vs %d" % (kd, kb))
+    if out is None:
+        out = torch.empty(m, n, dtype=out_dtype or a.dtype, device=a.device)
+    if m == 0 or n == 0:
+        return out
+    if kd == 0:
+        return out if accumulate else out.zero_()
+    bias = None if col_bias is None else col_bias.detach().float().contiguous()
+    with torch.cuda.device(a.device):
+        _lib.check(_lib.lib().sru_b200_gemm(
+            _lib.ptr(out), _lib.ptr(a), _lib.ptr(b), _lib.ptr(bias), m, n, kd,
+            a.stride(0), b.stride(0), out.stride(0), int(trans_a), int(trans_b),
+            _lib.DTYPE_CODE[a.dtype], _lib.DTYPE_CODE[out.dtype], int(accumulate),
+            _lib.current_stream_ptr(a.device)))
+    return out
+
+
+class _Projection(Function):
+    @staticmethod
+    def forward(ctx, x, w, col_bias):
+        # x (M, K), w (K, N), both already in the 16-bit compute dtype
+        ctx.save_for_backward(x, w)
+        ctx.has_bias = col_bias is not None
+        return gemm(x, w, col_bias=col_bias)
+
+    @staticmethod
+    def backward(ctx, grad_u):
+        x, w = ctx.saved_tensors
+        grad_u = grad_u.contiguous()
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            gx = gemm(grad_u, w, trans_b=True)            # (M,N) x (K,N)^T -> (M,K)
+        if ctx.needs_input_grad[1]:
+            gw = gemm(x, grad_u, trans_a=True)            # (M,K)^T x (M,N) -> (K,N)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            gb = grad_u.float().sum(0)
+        return gx, gw, gb
+
+
+def project(x: Tensor, w: Tensor, col_bias: Optional[Tensor] = None) -> Tensor:
+    """x (M, K) @ w (K, N) with autograd.  Follows autocast: inside an autocast region the
+    operands are cast to the autocast dtype, as ``Tensor.mm`` would be."""
+    if not x.is_cuda:
+        raise _lib.SruB200Error("sru_b200 has no CPU path: the projection input must be a CUDA tensor")
+    dt = x.dtype
+    if torch.is_autocast_enabled():
+        dt = torch.get_autocast_gpu_dtype()
+    elif w.dtype != x.dtype:
+        dt = w.dtype
+    if dt in _SIXTEEN and gemm_backend() == "tcgen05":
+        xc = x if x.dtype == dt else x.to(dt)
+        wc = w if w.dtype == dt else w.to(dt)
+        with torch.autocast("cuda", enabled=False):
+            return _Projection.apply(xc, wc, col_bias)
+    out = x.mm(w) if x.dtype == w.dtype or torch.is_autocast_enabled() else x.to(dt).mm(w)
+    if col_bias is not None:
+        out = out + col_bias.to(out.dtype)
+    return out

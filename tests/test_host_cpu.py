@@ -1,0 +1,100 @@
+"""CPU-only checks: the host-side mirror against the reference's golden vectors (through the
+oracle scan), the library's exported symbols, and argument validation that needs no GPU."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+from conftest import ROOT, rel_err
+from oracle.cpu_model import to_oracle
+from sru_b200 import _lib
+from sru_b200.modules import SRU, SRUCell
+
+
+def _build(case):
+    model = SRU(**case["kwargs"])
+    missing = model.load_state_dict(case["state"], strict=True)
+    assert not missing.missing_keys and not missing.unexpected_keys
+    return to_oracle(model)
+
+
+def test_state_dict_layout_and_init_match_reference(model_cases):
+    """Same seed -> same parameters as the reference's reset_parameters; same keys and shapes."""
+    seeds = {"config1": 0}
+    for case in model_cases:
+        if case["name"] not in seeds:
+            continue
+        torch.manual_seed(seeds[case["name"]])
+        model = SRU(**case["kwargs"])
+        sd = model.state_dict()
+        assert list(sd.keys()) == list(case["state"].keys())
+        for k, v in case["state"].items():
+            assert sd[k].shape == v.shape
+            assert torch.equal(sd[k], v), k
+
+
+def test_model_cases_through_oracle(model_cases):
+    """Layer plumbing (LN placement, residual, c0 split, projection, compat return) is the reference's."""
+    for case in model_cases:
+        model = _build(case)
+        model.train()
+        h, c = model(case["x"], case["c0"], mask_pad=case["mask_pad"])
+        (h.sum() if case["loss"] == "sum" else (h ** 2).mean()).backward()
+        assert (h - case["h"]).abs().max() <= 1e-5, case["name"]
+        assert (c - case["c"]).abs().max() <= 1e-5, case["name"]
+        for n, p in model.named_parameters():
+            if n in case["grads"]:
+                assert rel_err(p.grad, case["grads"][n]) <= 2e-5, (case["name"], n)
+
+
+def test_regression_artifact_through_oracle(regression_case):
+    """The reference's own regression vector (sru 2.3.5): outputs within 1e-6."""
+    rc = regression_case
+    model = SRU(**rc["kwargs"]).eval()
+    model.load_state_dict(rc["state"], strict=True)
+    model = to_oracle(model).eval()
+    with torch.enable_grad():
+        h, c = model(rc["x"])
+    assert (h - rc["h"]).abs().max() <= 1e-6
+    assert (c - rc["c"]).abs().max() <= 1e-6
+
+
+def test_cell_geometry():
+    cell = SRUCell(6, 8, bidirectional=True, n_proj=4)
+    assert cell.num_matrices == 4 and cell.projection_size == 4
+    assert cell.weight.shape == (4, 16 * 4) and cell.weight_proj.shape == (6, 4)
+    assert cell.weight_c.shape == (32,) and cell.bias.shape == (32,)
+    cell = SRUCell(8, 8, n_proj=8)
+    assert cell.projection_size == 0 and cell.num_matrices == 3
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "sru_b200.h")).read()
+    names = sorted(set(re.findall(r"\b(sru_b200_[a-z0-9_]+)\s*\(", header)))
+    assert len(names) >= 7
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    for n in names:
+        assert hasattr(lib, n), n
+    assert lib.sru_b200_version() >= 100
+
+
+def test_argument_validation_without_gpu():
+    L = _lib.lib()
+    rc = L.sru_b200_scan_forward(None, None, None, None, None, None, None, None, None, None,
+                                 4, 2, 8, 1, 5, 0, 1, 0, 1.0, 0, 0, None)
+    assert rc == -1 and b"k must be 3 or 4" in L.sru_b200_last_error()
+    rc = L.sru_b200_scan_forward(None, None, None, None, None, None, None, None, None, None,
+                                 4, 2, 8, 1, 3, 0, 1, 0, 1.0, 2, 1, None)
+    assert rc == -1 and b"c_dtype" in L.sru_b200_last_error()
+    assert L.sru_b200_scan_backward_workspace_bytes(10, 4, 8, 2, 3, 0) == 4 * 4 * 16 * 4
+
+
+def test_cpu_tensors_are_refused():
+    from sru_b200 import ops
+    with pytest.raises(_lib.SruB200Error):
+        ops.elementwise_recurrence_gpu(torch.zeros(2, 1, 24), torch.zeros(2, 1, 8), torch.zeros(16),
+                                       torch.zeros(16), torch.zeros(1, 8), 0, 8, False, True)
+    with pytest.raises(_lib.SruB200Error):
+        SRU(8, 8)(torch.zeros(2, 1, 8))

@@ -1,0 +1,175 @@
+"""Model-level parity on the GPU: SRU / SRUCell of this package against the reference's golden
+vectors and against the CPU oracle model, eager and TorchScript, fp32 and autocast."""
+import pytest
+import torch
+
+from conftest import rel_err
+from oracle.cpu_model import to_oracle
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _sru():
+    from sru_b200.modules import SRU
+    return SRU
+
+
+def _loss(h, kind):
+    return h.sum() if kind == "sum" else (h ** 2).mean()
+
+
+def test_golden_model_cases(model_cases):
+    """Forward, last states and every parameter gradient of the reference's sru.SRU (CPU, fp32);
+    the absolute bound 1e-4 is the reference's own CPU-vs-GPU test bound (test/sru/test_sru.py:129)."""
+    SRU = _sru()
+    for case in model_cases:
+        model = SRU(**case["kwargs"])
+        model.load_state_dict(case["state"], strict=True)
+        model = model.to(DEV).train()
+        mp = None if case["mask_pad"] is None else case["mask_pad"].to(DEV)
+        c0 = None if case["c0"] is None else case["c0"].to(DEV)
+        h, c = model(case["x"].to(DEV), c0, mask_pad=mp)
+        _loss(h, case["loss"]).backward()
+        assert h.dtype == torch.float32 and c.dtype == torch.float32
+        assert (h.cpu() - case["h"]).abs().max() <= 1e-4, case["name"]
+        assert (c.cpu() - case["c"]).abs().max() <= 1e-4, case["name"]
+        assert rel_err(h, case["h"]) <= 1e-5 and rel_err(c, case["c"]) <= 1e-5, case["name"]
+        for n, p in model.named_parameters():
+            if n in case["grads"]:
+                assert (p.grad.cpu() - case["grads"][n]).abs().max() <= 1e-4, (case["name"], n)
+                assert rel_err(p.grad, case["grads"][n]) <= 2e-5, (case["name"], n)
+
+
+def test_regression_artifact(regression_case):
+    """Golden vector of sru 2.3.5 (test/regression/test_regression.py:19-51), bound 1e-6."""
+    rc = regression_case
+    model = _sru()(**rc["kwargs"]).eval()
+    model.load_state_dict(rc["state"], strict=True)
+    model = model.to(DEV)
+    with torch.no_grad():
+        h, c = model(rc["x"].to(DEV))
+    assert (h.cpu() - rc["h"]).abs().max() <= 1e-6
+    assert (c.cpu() - rc["c"]).abs().max() <= 1e-6
+
+
+@pytest.mark.parametrize("bidirectional", [False, True])
+@pytest.mark.parametrize("layer_norm", [False, True])
+def test_batch_independence(bidirectional, layer_norm):
+    """Final state of a padded batch equals each sequence run alone (test/sru/test_sru.py:6-78)."""
+    torch.manual_seed(3)
+    model = _sru()(7, 4, num_layers=5, bidirectional=bidirectional, layer_norm=layer_norm).to(DEV).eval()
+    lens = [4, 2, 3]
+    L = max(lens)
+    x = torch.randn(L, len(lens), 7, device=DEV)
+    mp = torch.tensor([[t >= n for n in lens] for t in range(L)], device=DEV)
+    for grad in (False, True):
+        with torch.set_grad_enabled(grad):
+            _, c = model(x, mask_pad=mp)
+            for i, n in enumerate(lens):
+                _, ci = model(x[:n, i:i + 1].contiguous())
+                assert (c[:, i] - ci[:, 0]).abs().max() <= 1e-4
+
+
+@pytest.mark.parametrize("bidirectional", [False, True])
+@pytest.mark.parametrize("proj", [0, 4])
+@pytest.mark.parametrize("layer_norm", [False, True])
+def test_torchscript_equals_eager(bidirectional, proj, layer_norm):
+    """eager(grad) == eager(no_grad) == scripted (test/sru/test_torchscript.py:6-53), bound 1e-4."""
+    torch.manual_seed(5)
+    model = _sru()(32, 32, num_layers=2, bidirectional=bidirectional, rescale=True, projection_size=proj,
+                   layer_norm=layer_norm).to(DEV).eval()
+    x = torch.randn(16, 8, 32, device=DEV)
+    h1, c1 = model(x)
+    with torch.no_grad():
+        h2, c2 = model(x)
+        ts = torch.jit.script(model)
+        h3, c3 = ts(x)
+    for a, b in ((h1, h2), (c1, c2), (h1, h3), (c1, c3)):
+        assert (a - b).abs().max() <= 1e-4
+
+
+@pytest.mark.parametrize("amp_dtype", [torch.bfloat16, torch.float16])
+def test_autocast_native_and_reference_modes(amp_dtype):
+    """Autocast training step: both amp modes return what the reference returns in dtype
+    (fp32 h and c, fp32 parameter gradients), and values within 2e-2 of the fp32 CPU oracle
+    that is fed the same 16-bit-rounded weights and input."""
+    import sru_b200
+    torch.manual_seed(11)
+    SRU = _sru()
+    kw = dict(input_size=64, hidden_size=64, num_layers=3, bidirectional=True, layer_norm=True, rescale=True,
+              dropout=0.0)
+    model = SRU(**kw).to(DEV).train()
+    L, B = 24, 6
+    x = torch.randn(L, B, 64, device=DEV)
+    lens = torch.randint(12, L + 1, (B,))
+    mp = (torch.arange(L).view(L, 1) >= lens.view(1, B)).to(DEV)
+    cpu = to_oracle(model).train()
+    h_ref, c_ref = cpu(x.cpu(), mask_pad=mp.cpu())
+    h_ref.sum().backward()
+    ref_grads = {n: p.grad for n, p in cpu.named_parameters()}
+    for mode in ("native", "reference"):
+        sru_b200.set_amp_mode(mode)
+        try:
+            model.zero_grad()
+            with torch.autocast("cuda", dtype=amp_dtype):
+                h, c = model(x, mask_pad=mp)
+                loss = h.float().sum()
+            loss.backward()
+        finally:
+            sru_b200.set_amp_mode("native")
+        assert h.dtype == torch.float32 and c.dtype == torch.float32, mode
+        assert rel_err(h, h_ref) <= 2e-2, (mode, rel_err(h, h_ref))
+        assert rel_err(c, c_ref) <= 2e-2, mode
+        for n, p in model.named_parameters():
+            assert p.grad.dtype == torch.float32
+            assert rel_err(p.grad, ref_grads[n]) <= 2e-2, (mode, n, rel_err(p.grad, ref_grads[n]))
+
+
+def test_dropout_mask_is_an_input():
+    """With the same RNG state the training-mode dropout mask equals the oracle model's."""
+    torch.manual_seed(2)
+    model = _sru()(16, 16, num_layers=3, dropout=0.3).to(DEV).train()
+    x = torch.randn(9, 4, 16, device=DEV)
+    masks = []
+    orig = type(model.rnn_lst[0]).get_dropout_mask_
+
+    def record(self, size, p):
+        m = orig(self, size, p)
+        masks.append(m.cpu())
+        return m
+
+    cpu = to_oracle(model).train()
+    it = iter(masks)
+    for cell in model.rnn_lst:
+        cell.get_dropout_mask_ = record.__get__(cell)
+    h, c = model(x)
+    for cell in cpu.rnn_lst:
+        cell.get_dropout_mask_ = (lambda size, p, _it=it: next(_it))
+    h_ref, c_ref = cpu(x.cpu())
+    assert len(masks) == 2  # no dropout after the last layer
+    assert rel_err(h, h_ref) <= 1e-5 and rel_err(c, c_ref) <= 1e-5
+
+
+def test_sru_cuda_ops_backward_match_python_path():
+    """The registered sru_cuda::* backward operators against the ctypes path (same kernels)."""
+    from sru_b200 import _lib, ops
+    _lib.load_torch_ops()
+    g = torch.Generator().manual_seed(9)
+    L, B, d = 10, 3, 16
+    for bi in (False, True):
+        D = d * (2 if bi else 1)
+        U = torch.randn(L, B, D * 3, generator=g).to(DEV)
+        x = torch.randn(L, B, D, generator=g).to(DEV)
+        wc, bias = torch.randn(2 * D, generator=g).to(DEV), torch.randn(2 * D, generator=g).to(DEV)
+        c0 = torch.randn(B, D, generator=g).to(DEV)
+        gh, gl = torch.randn(L, B, D, generator=g).to(DEV), torch.randn(B, D, generator=g).to(DEV)
+        fwd = torch.ops.sru_cuda.sru_bi_forward_simple if bi else torch.ops.sru_cuda.sru_forward_simple
+        bwd = torch.ops.sru_cuda.sru_bi_backward_simple if bi else torch.ops.sru_cuda.sru_backward_simple
+        h, c = fwd(U, x, wc, bias, c0, None, None, L, B, d)
+        gu, gx, gwc, gb, gi = bwd(U, x, wc, bias, c0, None, None, c, gh, gl, L, B, d)
+        h2, c2, cl2 = ops.scan_forward(U, x, wc, bias, c0, None, None, L, B, d, 2 if bi else 1, 3, 0, 1, 0, 1.0)
+        r = ops.scan_backward(U, x, wc, bias, c0, None, None, c2, gh, gl, L, B, d, 2 if bi else 1, 3, 0, 1, 0, 1.0)
+        assert torch.equal(h, h2) and torch.equal(c, c2)
+        assert torch.equal(gu, r[0]) and torch.equal(gx, r[1]) and torch.equal(gi, r[4])
+        assert torch.equal(gwc.sum(1).view(-1), r[2]) and torch.equal(gb.sum(1).view(-1), r[3])

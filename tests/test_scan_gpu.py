@@ -1,0 +1,240 @@
+"""Parity of the CUDA scan kernels (called through the C ABI) with the CPU oracle.
+
+Tolerances (relative to the largest magnitude of the reference tensor):
+  fp64 1e-10, fp32 1e-5, bf16 / fp16 2e-2.
+For 16-bit storage the oracle runs in fp32 on the same 16-bit-rounded inputs.
+"""
+import os
+
+import pytest
+import torch
+
+from conftest import rel_err
+from oracle import sru_oracle
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.float64: 1e-10, torch.float32: 1e-5, torch.bfloat16: 2e-2, torch.float16: 2e-2}
+
+
+def _ops():
+    from sru_b200 import ops
+    return ops
+
+
+class _env:
+    def __init__(self, **kw):
+        self.kw = {k: str(v) for k, v in kw.items() if v is not None}
+
+    def __enter__(self):
+        self.old = {k: os.environ.get(k) for k in self.kw}
+        os.environ.update(self.kw)
+
+    def __exit__(self, *a):
+        for k, v in self.old.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
+
+
+def run_both(case_inputs, dtype, c_dtype=None, need_grad=True):
+    """Runs oracle (CPU) and CUDA on the same (dtype-rounded) inputs; returns two dicts."""
+    ops = _ops()
+    (U, x, wc, bias, c0, mc, mp, gh, gl, L, B, d, dirs, k, act, skip, custom, scale) = case_inputs
+    dev = torch.device("cuda:0")
+    odt = torch.float64 if dtype == torch.float64 else torch.float32
+    sm = odt
+    Us, xs = U.to(dtype), x.to(dtype)
+    wcs = wc.to(dtype) if custom else wc.to(sm)
+    ghs = gh.to(dtype)
+    # oracle on the rounded values
+    oh, och, ocl = sru_oracle.forward(Us.to(odt), xs.to(odt), wcs.to(odt), bias.to(odt), c0.to(odt),
+                                      None if mc is None else mc.to(odt), mp, L, B, d, dirs, k, act, skip,
+                                      custom, scale)
+    ref = dict(h=oh, c_last=ocl, c_hist=och)
+    D = d * dirs
+    cu = lambda t: None if t is None else t.to(dev).contiguous()
+    pad = None if mp is None else mp.bool().to(dev).contiguous()
+    h, c_hist, c_last = ops.scan_forward(cu(Us), cu(xs) if skip == 1 else None, cu(wcs), cu(bias.to(sm)),
+                                         cu(c0.to(sm)), cu(None if mc is None else mc.to(sm)), pad,
+                                         L, B, d, dirs, k, act, skip, int(custom), scale, True, c_dtype)
+    out = dict(h=h, c_last=c_last, c_hist=c_hist)
+    if need_grad:
+        # the oracle's backward consumes ITS c history; the kernel consumes its own
+        ogu, ogx, ogwc, ogb, ogi = sru_oracle.backward(
+            Us.to(odt), xs.to(odt), wcs.to(odt), bias.to(odt), c0.to(odt),
+            None if mc is None else mc.to(odt), mp, och, ghs.to(odt), gl.to(odt),
+            L, B, d, dirs, k, act, skip, custom, scale)
+        ref.update(grad_u=ogu, grad_x=ogx, grad_wc=ogwc, grad_bias=ogb, grad_init=ogi)
+        gu, gx, gwc, gb, gi = ops.scan_backward(
+            cu(Us), cu(xs) if skip == 1 else None, cu(wcs), cu(bias.to(sm)), cu(c0.to(sm)),
+            cu(None if mc is None else mc.to(sm)), pad, c_hist, cu(ghs), cu(gl.to(sm)),
+            L, B, d, dirs, k, act, skip, int(custom), scale)
+        out.update(grad_u=gu, grad_x=gx, grad_wc=gwc, grad_bias=gb, grad_init=gi)
+    torch.cuda.synchronize()
+    from sru_b200 import _lib
+    _lib.check_device_error()
+    return out, ref
+
+
+def compare(out, ref, tol, tag):
+    for key, r in ref.items():
+        if r is None:
+            assert out[key] is None, (tag, key)
+            continue
+        e = rel_err(out[key].reshape(r.shape), r)
+        assert e <= tol, (tag, key, e)
+
+
+def golden_inputs(case, ):
+    m = case["meta"]
+    skip = 0 if not m["has_skip"] else (1 if m["k"] == 3 else 2)
+    return (case["U"], case["x"], case["weight_c"], case["bias"], case["c_init"], case["mask_c"],
+            case["mask_pad"], case["grad_h"], case["grad_last"], m["L"], m["B"], m["d"], m["dirs"],
+            m["k"], m["act"], skip, bool(m["custom"]), 1.0 if m["scale"] is None else m["scale"])
+
+
+def random_inputs(L, B, d, dirs, k, skip=None, pad=None, maskc=True, c0=True, scale=1.0, seed=0,
+                  custom=False, act=0):
+    g = torch.Generator().manual_seed(seed)
+    D = d * dirs
+    if skip is None:
+        skip = 1 if k == 3 else 2
+    U = torch.randn(L, B, D * k, generator=g)
+    x = torch.randn(L, B, D, generator=g)
+    wc = torch.randn(L, B, D * 2, generator=g) if custom else torch.randn(2 * D, generator=g)
+    bias = torch.randn(2 * D, generator=g)
+    c0t = torch.randn(B, D, generator=g) if c0 else torch.zeros(B, D)
+    mc = ((torch.rand(B, D, generator=g) > 0.2).float() / 0.8) if maskc else None
+    mp = None
+    if pad == "tail":
+        lens = torch.randint(max(1, L // 2), L + 1, (B,), generator=g)
+        mp = torch.arange(L).view(L, 1) >= lens.view(1, B)
+    elif pad == "random":
+        mp = torch.rand(L, B, generator=g) > 0.7
+    gh = torch.randn(L, B, D, generator=g)
+    gl = torch.randn(B, D, generator=g)
+    return (U, x, wc, bias, c0t, mc, mp, gh, gl, L, B, d, dirs, k, act, skip, custom, scale)
+
+
+@pytest.mark.parametrize("dtype", [torch.float64, torch.float32])
+@pytest.mark.parametrize("force_generic", [0, 1])
+def test_golden_cases(op_cases, dtype, force_generic):
+    """Golden vectors of the reference's elementwise_recurrence_naive, outputs and all gradients."""
+    with _env(SRU_B200_FORCE_GENERIC=force_generic):
+        for case in op_cases:
+            inp = golden_inputs(case)
+            out, _ = run_both(inp, dtype)
+            tol = TOL[dtype]
+            gold = dict(h=case["h"], c_last=case["c_last"], grad_u=case["grad_U"], grad_x=case["grad_x"],
+                        grad_wc=case["grad_weight_c"], grad_bias=case["grad_bias"],
+                        grad_init=case["grad_c_init"])
+            compare({k: out[k] for k in gold}, gold, tol, case["name"])
+
+
+SHAPES = [
+    # L,  B,  d,  dirs, k, pad
+    (9,   3,  8,   1, 3, None),
+    (13,  5,  16,  2, 3, "tail"),
+    (7,   4,  32,  2, 4, "random"),
+    (33,  7,  64,  1, 3, "tail"),
+    (20,  32, 128, 1, 3, None),       # first benchmark configuration's layer shape
+    (17,  9,  304, 1, 3, "tail"),     # hidden size of the reference's AMP test (not a power of two)
+    (41,  6,  128, 2, 4, "tail"),
+    (5,   33, 256, 2, 3, "random"),
+    (64,  2,  512, 1, 3, None),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_pipelined_vs_oracle(shape, dtype):
+    L, B, d, dirs, k, pad = shape
+    inp = random_inputs(L, B, d, dirs, k, pad=pad, scale=1.3, seed=L * 131 + B)
+    for c_dtype in ([None] if dtype == torch.float32 else [torch.float32, dtype]):
+        out, ref = run_both(inp, dtype, c_dtype)
+        compare(out, ref, TOL[dtype], (shape, dtype, c_dtype))
+
+
+@pytest.mark.parametrize("v", [1, 2, 4, 8])
+@pytest.mark.parametrize("threads", [32, 64, 128])
+@pytest.mark.parametrize("stages", [2, 5])
+def test_pipelined_tilings(v, threads, stages):
+    """Every columns-per-thread / CTA size / ring depth the dispatcher can pick gives the same answer."""
+    for dtype in (torch.float32, torch.bfloat16):
+        s = 4 if dtype == torch.float32 else 2
+        if v * s > 16 or v * s < 4:
+            continue
+        for (L, B, d, dirs, k, pad) in [(11, 5, 64, 2, 3, "tail"), (6, 3, 128, 1, 4, "random")]:
+            inp = random_inputs(L, B, d, dirs, k, pad=pad, seed=v * 7 + threads)
+            with _env(SRU_B200_FWD_V=v, SRU_B200_BWD_V=v, SRU_B200_SCAN_THREADS=threads,
+                      SRU_B200_SCAN_STAGES=stages):
+                out, ref = run_both(inp, dtype)
+            compare(out, ref, TOL[dtype], (v, threads, stages, dtype, L, B, d, dirs, k))
+
+
+def test_options_no_skip_no_bias_no_c0():
+    ops = _ops()
+    inp = list(random_inputs(10, 4, 64, 2, 3, skip=0, pad="tail", maskc=False, c0=False, seed=5))
+    out, ref = run_both(tuple(inp), torch.float32)
+    compare(out, ref, 1e-5, "noskip")
+    # bias == NULL means "already folded into U": equal to a zero bias
+    (U, x, wc, bias, c0, mc, mp, gh, gl, L, B, d, dirs, k, act, skip, custom, scale) = inp
+    dev = "cuda:0"
+    h0, _, cl0 = ops.scan_forward(U.to(dev), None, wc.to(dev), torch.zeros_like(bias).to(dev), None, None,
+                                  mp.to(dev), L, B, d, dirs, k, act, skip, 0, 1.0)
+    h1, _, cl1 = ops.scan_forward(U.to(dev), None, wc.to(dev), None, None, None,
+                                  mp.to(dev), L, B, d, dirs, k, act, skip, 0, 1.0)
+    assert torch.equal(h0, h1) and torch.equal(cl0, cl1)
+
+
+def test_inference_without_history_matches():
+    ops = _ops()
+    inp = random_inputs(37, 6, 128, 1, 3, pad=None, seed=11)
+    (U, x, wc, bias, c0, mc, mp, gh, gl, L, B, d, dirs, k, act, skip, custom, scale) = inp
+    dev = "cuda:0"
+    a = ops.scan_forward(U.to(dev), x.to(dev), wc.to(dev), bias.to(dev), c0.to(dev), None, None,
+                         L, B, d, dirs, k, act, skip, 0, 1.0, True)
+    b = ops.scan_forward(U.to(dev), x.to(dev), wc.to(dev), bias.to(dev), c0.to(dev), None, None,
+                         L, B, d, dirs, k, act, skip, 0, 1.0, False)
+    assert b[1] is None and torch.equal(a[0], b[0]) and torch.equal(a[2], b[2])
+    # last state equals the last row of the history
+    assert torch.equal(a[1][-1], a[2])
+
+
+def test_bad_arguments_are_reported():
+    from sru_b200 import _lib
+    L = _lib.lib()
+    rc = L.sru_b200_scan_forward(None, None, None, None, None, None, None, None, None, None,
+                                 4, 2, 8, 3, 3, 0, 1, 0, 1.0, 0, 0, None)
+    assert rc == -1 and b"dirs" in L.sru_b200_last_error()
+    rc = L.sru_b200_scan_forward(None, None, None, None, None, None, None, None, None, None,
+                                 4, 2, 8, 1, 4, 0, 1, 0, 1.0, 0, 0, None)
+    assert rc == -1 and b"skip_type 1" in L.sru_b200_last_error()
+    rc = L.sru_b200_scan_backward(*([None] * 15), 4, 2, 8, 1, 3, 0, 1, 0, 1.0, 0, 0, None, 0, None)
+    assert rc == -1
+
+
+def test_autograd_function_matches_oracle_autograd():
+    """elementwise_recurrence_gpu (public operator) against the oracle through torch.autograd."""
+    ops = _ops()
+    for bi, k in ((False, 3), (True, 4), (True, 3)):
+        dirs = 2 if bi else 1
+        L, B, d = 12, 5, 32
+        inp = random_inputs(L, B, d, dirs, k, pad="tail", scale=1.4, seed=77 + k)
+        (U, x, wc, bias, c0, mc, mp, gh, gl, *_rest) = inp
+        leaves = [t.clone().requires_grad_(True) for t in (U, x, wc, bias, c0)]
+        sx = torch.tensor([1.4])
+        h, cl = sru_oracle.elementwise_recurrence_oracle(*leaves, 0, d, bi, True, sx, mc, mp)
+        ((h * gh).sum() + (cl * gl).sum()).backward()
+        dev = "cuda:0"
+        gleaves = [t.detach().clone().to(dev).requires_grad_(True) for t in (U, x, wc, bias, c0)]
+        h2, cl2 = ops.elementwise_recurrence_gpu(*gleaves, 0, d, bi, True, sx.to(dev), mc.to(dev), mp.to(dev))
+        ((h2 * gh.to(dev)).sum() + (cl2 * gl.to(dev)).sum()).backward()
+        assert rel_err(h2, h) <= 1e-5 and rel_err(cl2, cl) <= 1e-5
+        for a, b, name in zip(gleaves, leaves, "U x wc bias c0".split()):
+            if k == 4 and name == "x":
+                assert a.grad is None or float(a.grad.abs().max()) == 0.0
+                continue
+            assert rel_err(a.grad, b.grad) <= 1e-5, (bi, k, name)
