@@ -1,0 +1,420 @@
+#!/usr/bin/env python
+"""Benchmark of the SRU hot path on B200: forward+backward tokens/s of a batch-sharded
+training step (projection GEMMs + light-recurrence scans + per-layer gradient all-reduce).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config 5] [--impl ours|reference]
+
+One process per GPU (torchrun for N > 1).  Rank 0 prints ONE JSON line.  `value` is measured
+with inputs resident in HBM; `e2e` is the same step through the public module API with the
+step's input copied from pinned host memory and the loss read back inside the timed region.
+`roofline` describes the kernel class that takes the most time (CUDA events around every
+C-ABI launch in a separate instrumented pass); `kernels` lists every class.  `cpu_baseline`
+(N = 1 only) times the CPU oracle model on a bounded sample of the same workload.
+`--impl reference` times that CPU implementation instead, with all host threads.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# The five workloads (shapes and distributions of the benchmark definition; synthetic data).
+CONFIGS = {
+    1: dict(name="config1: 2-layer uni SRU 128->128, fp32, L=20 B=32", L=20, B=32, amp=None,
+            kwargs=dict(input_size=128, hidden_size=128, num_layers=2, dropout=0.0, highway_bias=-2.0,
+                        layer_norm=False), x_std=1.0, lens=None, loss="sum", train=True),
+    2: dict(name="config2: 4-layer bi SRU 512->512/dir, layer_norm, rescale, bf16 autocast, L=256 B=64, mask_pad",
+            L=256, B=64, amp=torch.bfloat16,
+            kwargs=dict(input_size=512, hidden_size=512, num_layers=4, bidirectional=True, layer_norm=True,
+                        rescale=True), x_std=1.0, lens=(128, 256), loss="sum", train=True),
+    3: dict(name="config3: 6-layer uni SRU 2048, projection 512, highway_bias -3, fp16 autocast, L=512 B=32",
+            L=512, B=32, amp=torch.float16,
+            kwargs=dict(input_size=2048, hidden_size=2048, num_layers=6, projection_size=512,
+                        highway_bias=-3.0), x_std=0.5, lens=None, loss="meansq", train=True, c0=True),
+    4: dict(name="config4: 1-layer uni SRU 1024, bf16, L=8192 B=16, inference", L=8192, B=16, amp=None,
+            kwargs=dict(input_size=1024, hidden_size=1024, num_layers=1), x_std=1.0, lens=None, loss=None,
+            train=False, param_dtype=torch.bfloat16),
+    5: dict(name="config5: 12-layer bi SRU 120->1024/dir, dropout 0.1, bf16 autocast, L=1000 B=256, mask_pad",
+            L=1000, B=256, amp=torch.bfloat16,
+            kwargs=dict(input_size=120, hidden_size=1024, num_layers=12, bidirectional=True, dropout=0.1),
+            x_std=1.0, lens=(600, 1000), loss="meansq", train=True),
+}
+
+
+def make_inputs(cfg, cfg_id, B, batch_offset=0):
+    """Seeded synthetic inputs on the CPU: x ~ N(0, x_std), tail padding from uniform lengths."""
+    g = torch.Generator().manual_seed(1000 + cfg_id)
+    L, Bfull = cfg["L"], cfg["B"]
+    x = torch.randn(L, Bfull, cfg["kwargs"]["input_size"], generator=g) * cfg["x_std"]
+    mask = None
+    if cfg["lens"] is not None:
+        lo, hi = cfg["lens"]
+        lens = torch.randint(lo, hi + 1, (Bfull,), generator=g)
+        mask = torch.arange(L).view(L, 1) >= lens.view(1, Bfull)
+    x = x[:, batch_offset:batch_offset + B].contiguous()
+    if mask is not None:
+        mask = mask[:, batch_offset:batch_offset + B].contiguous()
+    return x, mask
+
+
+def layer_shapes(kwargs):
+    """[(in, D, k, dirs, proj)] per layer, as sru/modules.py:126-133,551-568 derive them."""
+    dirs = 2 if kwargs.get("bidirectional") else 1
+    D = kwargs["hidden_size"] * dirs
+    out = []
+    for i in range(kwargs.get("num_layers", 2)):
+        n_in = kwargs["input_size"] if i == 0 else D
+        k = 4 if (kwargs.get("has_skip_term", True) and n_in != D) else 3
+        p = kwargs.get("projection_size", 0)
+        p = p if 0 < p < min(n_in, D) else 0
+        out.append((n_in, D, k, dirs, p))
+    return out
+
+
+def algorithmic_work(cfg, B, s_bytes, c_bytes):
+    """Bytes of the scans and flops of the GEMMs for one step on B sequences.
+
+    Per column-step: forward (training) reads U[k] (+x when k=3) and writes h and c:
+    (k + e3 + 1)*s + c_bytes; inference (no c history) (k + e3 + 1)*s; backward reads U[k], x,
+    c, grad_h and writes grad_U[k], grad_x: (2k + 2*e3 + 1)*s + c_bytes.  GEMM flops:
+    2*M*K*N per product, backward = dgrad + wgrad (no dgrad for the first layer's input).
+    """
+    L = cfg["L"]
+    fwd = bwd = 0
+    flops_f = flops_b = 0
+    for li, (n_in, D, k, dirs, p) in enumerate(layer_shapes(cfg["kwargs"])):
+        cols = L * B * D
+        e3 = 1 if k == 3 else 0
+        if cfg["train"]:
+            fwd += cols * ((k + e3 + 1) * s_bytes + c_bytes)
+            bwd += cols * ((2 * k + 2 * e3 + 1) * s_bytes + c_bytes)
+        else:
+            fwd += cols * (k + e3 + 1) * s_bytes
+        M = L * B
+        f = 2 * M * (n_in * p + p * D * k) if p else 2 * M * n_in * D * k
+        flops_f += f
+        if cfg["train"]:
+            flops_b += 2 * f if li > 0 else (2 * f - (2 * M * n_in * (p if p else D * k)))
+    return dict(scan_fwd_bytes=fwd, scan_bwd_bytes=bwd, gemm_fwd_flops=flops_f, gemm_bwd_flops=flops_b)
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz, mx, reasons = [], 0, set()
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                mhz.append(float(r[0])); mx = max(mx, float(r[1]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not mhz:
+            return None
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return dict(hbm_gbs=d["hbm_gbs"], tflops_burst=d["bf16_tflops"], tflops_sustained=d["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm_gbs=6650.0, tflops_burst=1590.0, tflops_sustained=1400.0, source="fallback")
+
+
+def build_model(cfg, device):
+    from sru_b200.modules import SRU
+    torch.manual_seed(0)
+    model = SRU(**cfg["kwargs"])
+    if cfg.get("param_dtype") is not None:
+        model = model.to(cfg["param_dtype"])
+    model = model.to(device)
+    model.train(cfg["train"])
+    return model
+
+
+def run_step(model, cfg, x, mask, c0, tokens_global, reducer=None):
+    """One step on device-resident inputs.  Returns the loss tensor (or h for inference)."""
+    if not cfg["train"]:
+        with torch.no_grad():
+            h, c = model(x, c0, mask_pad=mask)
+        return c
+    if reducer is not None:
+        reducer.zero_grad()
+    else:
+        model.zero_grad(set_to_none=True)
+    amp = cfg["amp"]
+    with torch.autocast("cuda", dtype=amp, enabled=amp is not None):
+        h, c = model(x, c0, mask_pad=mask)
+    D = h.size(-1)
+    if cfg["loss"] == "sum":
+        loss = h.float().sum()
+    else:
+        loss = (h.float() ** 2).sum() / float(tokens_global * D)
+    loss.backward()
+    if reducer is not None:
+        reducer.finish()
+    return loss.detach()
+
+
+def cpu_baseline(cfg, cfg_id, threads, sample_B, steps=1, warmup=0):
+    """Times the CPU oracle model (restatement of the reference's CPU path) on sample_B sequences."""
+    from oracle import sru_oracle
+    from oracle.cpu_model import to_oracle
+    from sru_b200.modules import SRU
+    torch.set_num_threads(threads)
+    sru_oracle.set_threads(threads)
+    torch.manual_seed(0)
+    model = to_oracle(SRU(**cfg["kwargs"]))
+    model.train(cfg["train"])
+    x, mask = make_inputs(cfg, cfg_id, sample_B)
+    tokens = cfg["L"] * sample_B
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        if cfg["train"]:
+            model.zero_grad(set_to_none=True)
+            h, c = model(x, mask_pad=mask)
+            loss = h.sum() if cfg["loss"] == "sum" else (h ** 2).sum() / float(tokens * h.size(-1))
+            loss.backward()
+        else:
+            with torch.no_grad():
+                model(x, mask_pad=mask)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    return tokens, times
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--config", type=int, default=5, choices=sorted(CONFIGS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-sample-batch", type=int, default=0)
+    args = ap.parse_args()
+    cfg = CONFIGS[args.config]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    metric = "sru_fwd_bwd_tokens_per_sec" if cfg["train"] else "sru_fwd_tokens_per_sec"
+    host_cores = os.cpu_count() or 1
+    sample_B = args.cpu_sample_batch or {1: 32, 2: 4, 3: 1, 4: 1, 5: 1}[args.config]
+    sample_desc = "%s at batch %d of %d (all layers, full length, fp32 on CPU)" % (
+        cfg["name"].split(":")[0], sample_B, cfg["B"])
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        threads = host_cores
+        tokens, times = cpu_baseline(cfg, args.config, threads, sample_B, steps=max(1, args.steps),
+                                     warmup=min(args.warmup, 1))
+        ms = 1e3 * sum(times) / len(times)
+        val = tokens / (ms / 1e3)
+        print(json.dumps({
+            "impl": "reference", "metric": metric, "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": len(times), "warmup": min(args.warmup, 1), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": cfg["name"], "sample": sample_desc},
+            "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port",
+                             "sample": sample_desc},
+            "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }))
+        return
+
+    import torch.distributed as dist
+    from sru_b200 import _lib, ops
+    from sru_b200.distributed import LayerGradAllReducer, shard_batch
+    from sru_b200.projection import gemm_backend
+    _lib.lib()  # fail loudly here if the native library is missing
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    if world != args.gpus and rank == 0:
+        sys.stderr.write("warning: --gpus %d but WORLD_SIZE %d\n" % (args.gpus, world))
+
+    model = build_model(cfg, device)
+    x_cpu, mask_cpu = make_inputs(cfg, args.config, cfg["B"])
+    x_cpu = shard_batch(x_cpu, rank, world)
+    mask_cpu = shard_batch(mask_cpu, rank, world)
+    if cfg.get("param_dtype") is not None:
+        x_cpu = x_cpu.to(cfg["param_dtype"])
+    B_local = x_cpu.size(1)
+    tokens_global = cfg["L"] * cfg["B"]
+    x_pin = x_cpu.pin_memory()
+    mask_pin = None if mask_cpu is None else mask_cpu.pin_memory()
+    x_dev = x_pin.to(device)
+    mask_dev = None if mask_pin is None else mask_pin.to(device)
+    c0 = None
+    if cfg.get("c0"):
+        dirs = 2 if cfg["kwargs"].get("bidirectional") else 1
+        c0 = torch.zeros(cfg["kwargs"]["num_layers"], B_local, cfg["kwargs"]["hidden_size"] * dirs, device=device)
+    reducer = LayerGradAllReducer(model) if (cfg["train"] and world > 1) else None
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- warm-up ----
+    for _ in range(max(args.warmup, 3)):
+        run_step(model, cfg, x_dev, mask_dev, c0, tokens_global, reducer)
+    barrier()
+
+    # ---- timed: device-resident inputs ----
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    launches0 = _lib.launch_count
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        run_step(model, cfg, x_dev, mask_dev, c0, tokens_global, reducer)
+    e1.record()
+    barrier()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    launches = (_lib.launch_count - launches0) // max(1, args.steps)
+    clocks = sampler.stop() if sampler else None
+    ms_per_step = ms_total / args.steps
+    value = tokens_global / (ms_per_step / 1e3)
+
+    # ---- timed: end to end (pinned host input -> device, loss -> host) ----
+    barrier()
+    e0.record()
+    result_bytes = 0
+    for _ in range(args.steps):
+        xd = x_pin.to(device, non_blocking=True)
+        md = None if mask_pin is None else mask_pin.to(device, non_blocking=True)
+        out = run_step(model, cfg, xd, md, c0, tokens_global, reducer)
+        host = out.float().cpu()
+        result_bytes = host.numel() * host.element_size()
+    e1.record()
+    barrier()
+    ms_e2e = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    h2d = x_pin.numel() * x_pin.element_size() + (0 if mask_pin is None else mask_pin.numel())
+
+    # ---- instrumented pass: CUDA events around every C-ABI launch ----
+    _lib.timer = _lib.KernelTimer()
+    for _ in range(2):
+        run_step(model, cfg, x_dev, mask_dev, c0, tokens_global, reducer)
+    ksum = _lib.timer.summary()
+    _lib.timer = None
+    nprof = 2
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = measured_peaks()
+    s_bytes = 4 if (cfg["amp"] is None and cfg.get("param_dtype") is None) else 2
+    c_bytes = 4 if (s_bytes == 4 or ops._c_hist_dtype == "float32") else s_bytes
+    work = algorithmic_work(cfg, B_local, s_bytes, c_bytes)
+    kernels = {}
+    for name, (calls, ms) in ksum.items():
+        per_step_ms = ms / nprof
+        ent = {"launches_per_step": calls // nprof, "ms_per_step": per_step_ms}
+        if name in ("scan_fwd", "scan_fwd_infer"):
+            ent.update(bound="hbm", achieved=work["scan_fwd_bytes"] / (per_step_ms * 1e6), unit="GB/s",
+                       peak=peaks["hbm_gbs"])
+        elif name == "scan_bwd":
+            ent.update(bound="hbm", achieved=work["scan_bwd_bytes"] / (per_step_ms * 1e6), unit="GB/s",
+                       peak=peaks["hbm_gbs"])
+        ent["frac"] = ent["achieved"] / ent["peak"] if "achieved" in ent else None
+        kernels[name] = ent
+    gemm_ms = sum(v["ms_per_step"] for k, v in kernels.items() if k.startswith("gemm"))
+    if gemm_ms > 0:
+        fl = work["gemm_fwd_flops"] + work["gemm_bwd_flops"]
+        kernels["gemm_all"] = {"ms_per_step": gemm_ms, "bound": "tensor", "achieved": fl / (gemm_ms * 1e9),
+                               "unit": "TFLOP/s", "peak": peaks["tflops_sustained"],
+                               "frac": fl / (gemm_ms * 1e9) / peaks["tflops_sustained"]}
+    cands = {k: v for k, v in kernels.items() if v.get("frac") is not None and not (k.startswith("gemm_") and k != "gemm_all")}
+    roofline = None
+    if cands:
+        top = max(cands, key=lambda k: cands[k]["ms_per_step"])
+        t = cands[top]
+        roofline = {"kernel": top, "bound": t["bound"], "achieved": t["achieved"], "peak": t["peak"],
+                    "unit": t["unit"], "frac": t["frac"], "traffic": None, "peak_source": peaks["source"]}
+
+    out = {
+        "metric": metric, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32" if s_bytes == 4 else ("bf16" if (cfg["amp"] or cfg.get("param_dtype")) == torch.bfloat16 else "f16"),
+        "data": "synthetic",
+        "config": {"workload": cfg["name"], "global_batch": cfg["B"], "seq_len": cfg["L"],
+                   "parallelism": "batch-sharded dp%d" % world, "l2": "inputs larger than L2",
+                   "gemm": gemm_backend(), "c_hist": ops._c_hist_dtype, "amp_mode": ops.get_amp_mode()},
+        "e2e": {"value": tokens_global / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": result_bytes},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "roofline": roofline,
+        "kernels": kernels,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        tokens, times = cpu_baseline(cfg, args.config, host_cores, sample_B, steps=1, warmup=0)
+        out["cpu_baseline"] = {"value": tokens / times[0], "unit": "tokens/s", "cores": host_cores, "kind": "port",
+                               "sample": sample_desc}
+    print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

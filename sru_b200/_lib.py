@@ -82,3 +82,41 @@ def current_stream_ptr(device=None):
 
 def check_device_error(device=None):
     check(lib().sru_b200_check_device_error(current_stream_ptr(device)))
+
+
+class KernelTimer:
+    """Optional per-call timing with CUDA events on the launching stream (used by bench.py).
+
+    Install with ``_lib.timer = KernelTimer()``; every C-ABI launch made through ``call`` is then
+    bracketed by a pair of events recorded on the current stream.  ``summary()`` synchronises
+    and returns ``{name: (calls, total_ms)}``.
+    """
+
+    def __init__(self):
+        self.spans = {}
+
+    def add(self, name, start, end):
+        self.spans.setdefault(name, []).append((start, end))
+
+    def summary(self):
+        torch.cuda.synchronize()
+        return {k: (len(v), sum(s.elapsed_time(e) for s, e in v)) for k, v in self.spans.items()}
+
+
+timer = None          # a KernelTimer, or None
+launch_count = 0      # kernels of this library launched so far (bench.py reports the per-step figure)
+
+
+def call(name, n_kernels, fn, *args):
+    """Invoke a C-ABI entry point, count its kernel launches, time it if a timer is installed."""
+    global launch_count
+    launch_count += n_kernels
+    if timer is None:
+        return check(fn(*args))
+    start = torch.cuda.Event(enable_timing=True)
+    end = torch.cuda.Event(enable_timing=True)
+    start.record()
+    rc = fn(*args)
+    end.record()
+    timer.add(name, start, end)
+    return check(rc)

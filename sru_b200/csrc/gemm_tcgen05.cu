@@ -1,7 +1,394 @@
-// placeholder, replaced by the tcgen05 GEMM
+// Dense 16-bit GEMM on the 5th-generation tensor cores (tcgen05) for sm_100a.
+//
+//   C[M,N] = op(A)[M,K] * op(B)[K,N] (+ col_bias[N]) (+ C),   fp32 accumulation in tensor memory.
+//
+// One persistent CTA per SM, 192 threads, warp-specialised:
+//   warp 0     TMA producer: cp.async.bulk.tensor loads of 128B-swizzled A / B tiles into a
+//              4-stage shared-memory ring, completion counted on "full" mbarriers;
+//   warp 1     allocates tensor memory (512 columns = two 128x256 fp32 accumulators) and, with
+//              one elected thread, issues tcgen05.mma (M=128, N=256, K=16 per instruction,
+//              operands read straight from shared memory through matrix descriptors);
+//              tcgen05.commit releases ring stages and publishes finished accumulators;
+//   warps 2-5  epilogue: tcgen05.ld of the accumulator quarter each warp may address
+//              (TMEM lanes 32*(warp%4)..), bias / accumulate, conversion, 16-byte stores.
+// The two accumulators alternate between tiles, so the epilogue of tile i overlaps the MMAs
+// of tile i+1.  Tile order keeps N fastest, so the CTAs that run concurrently share A row
+// blocks and the whole B operand through L2.
+//
+// Operand layouts.  Both operands may be "K-major" (reduction index contiguous in memory) or
+// "MN-major" (the M / N index contiguous); the three products of the SRU layer need
+//   forward  U = x W           A K-major,  B MN-major
+//   dgrad    gx = gU W^T       A K-major,  B K-major
+//   wgrad    gW = x^T gU       A MN-major, B MN-major
+// and none of them needs a transposed copy.  Shared-memory tiles are the canonical 128-byte
+// swizzled layouts: K-major [rows][64 elements], 8-row groups 1024 B apart; MN-major slabs of
+// [64 k-rows][64 elements], 8-row groups 1024 B apart, successive 64-element chunks of the
+// M / N extent 8192 B apart.  No load uses cluster multicast.
+//
+// Every mbarrier wait is bounded; a wait that gives up raises the device error flag and the
+// CTA drains to its teardown, where tensor memory is released.
+#include <cudaTypedefs.h>
+
+#include <algorithm>
+
 #include "common.cuh"
-extern "C" int sru_b200_gemm(void *c, const void *a, const void *b, const float *col_bias, int64_t m,
-                             int64_t n, int64_t k_dim, int64_t lda, int64_t ldb, int64_t ldc, int trans_a,
-                             int trans_b, int ab_dtype, int c_dtype, int accumulate, void *stream) {
-    return srub::set_error(SRU_ERR_UNSUPPORTED, "gemm not built yet");
+
+namespace srub {
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int kStages = 4;
+constexpr int kAStage = BM * BK * 2;   // 16 KB
+constexpr int kBStage = BN * BK * 2;   // 32 KB
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 512;
+constexpr int kSmemBytes = kStages * (kAStage + kBStage) + 1024 /*align*/ + 256 /*barriers*/;
+
+struct GemmArgs {
+    void *c;
+    const float *bias;
+    int64_t M, N, K, ldc;
+    int c_dtype, accumulate;
+    int a_mn, b_mn;   // 1: MN-major operand
+    uint32_t idesc;
+    int tiles_m, tiles_n;
+    int *err;
+};
+
+// ---- PTX wrappers -----------------------------------------------------------------------
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+template <typename TO> __device__ __forceinline__ void store8(TO *dst, const float *v);
+template <> __device__ __forceinline__ void store8<float>(float *dst, const float *v) {
+    reinterpret_cast<float4 *>(dst)[0] = make_float4(v[0], v[1], v[2], v[3]);
+    reinterpret_cast<float4 *>(dst)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <> __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16 *dst, const float *v) {
+    uint4 o;
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0], v[1]), p1 = __floats2bfloat162_rn(v[2], v[3]);
+    __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4], v[5]), p3 = __floats2bfloat162_rn(v[6], v[7]);
+    o.x = *reinterpret_cast<uint32_t *>(&p0); o.y = *reinterpret_cast<uint32_t *>(&p1);
+    o.z = *reinterpret_cast<uint32_t *>(&p2); o.w = *reinterpret_cast<uint32_t *>(&p3);
+    *reinterpret_cast<uint4 *>(dst) = o;
+}
+template <> __device__ __forceinline__ void store8<__half>(__half *dst, const float *v) {
+    uint4 o;
+    __half2 p0 = __floats2half2_rn(v[0], v[1]), p1 = __floats2half2_rn(v[2], v[3]);
+    __half2 p2 = __floats2half2_rn(v[4], v[5]), p3 = __floats2half2_rn(v[6], v[7]);
+    o.x = *reinterpret_cast<uint32_t *>(&p0); o.y = *reinterpret_cast<uint32_t *>(&p1);
+    o.z = *reinterpret_cast<uint32_t *>(&p2); o.w = *reinterpret_cast<uint32_t *>(&p3);
+    *reinterpret_cast<uint4 *>(dst) = o;
+}
+
+// Epilogue of one 32-column chunk of one row: bias, optional accumulate, convert, store.
+template <typename TO>
+__device__ __forceinline__ void epilogue_chunk(const GemmArgs &g, const uint32_t (&r)[32], int64_t row, int64_t col0) {
+    TO *crow = reinterpret_cast<TO *>(g.c) + row * g.ldc + col0;
+#pragma unroll
+    for (int j0 = 0; j0 < 32; j0 += 8) {
+        if (col0 + j0 >= g.N) break;  // N is a multiple of 8
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[j0 + j]);
+        if (g.bias) {
+            const float4 b0 = *reinterpret_cast<const float4 *>(g.bias + col0 + j0);
+            const float4 b1 = *reinterpret_cast<const float4 *>(g.bias + col0 + j0 + 4);
+            v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+            v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+        }
+        if (g.accumulate) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] += Cvt<TO>::to_f(crow[j0 + j]);
+        }
+        store8<TO>(crow + j0, v);
+    }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const GemmArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment: the 128B swizzle pattern repeats every 1024 bytes of shared address
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *smem_a = smem;
+    uint8_t *smem_b = smem + kStages * kAStage;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kStages * (kAStage + kBStage));
+    const uint32_t bar_full = smem_u32(bars);             // [kStages]
+    const uint32_t bar_empty = bar_full + 8 * kStages;    // [kStages]
+    const uint32_t bar_tfull = bar_empty + 8 * kStages;   // [2]
+    const uint32_t bar_tempty = bar_tfull + 16;           // [2]
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ntiles = g.tiles_m * g.tiles_n;
+    const int nkb = (int)((g.K + BK - 1) / BK);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(bar_tfull + 8 * i, 1); mbar_init(bar_tempty + 8 * i, 4); }
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------- TMA producer -------------------------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+                const int mb = tile / g.tiles_n, nb = tile % g.tiles_n;
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1)) { atomicExch(g.err, 11); ok = false; break; }
+                    const uint32_t full = bar_full + 8 * stage;
+                    mbar_arrive_expect_tx(full, kAStage + kBStage);
+                    const uint32_t sa = smem_u32(smem_a + stage * kAStage);
+                    const uint32_t sb = smem_u32(smem_b + stage * kBStage);
+                    if (!g.a_mn) {
+                        tma_load_2d(sa, &map_a, full, kb * BK, mb * BM);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BM / 64; ++j)
+                            tma_load_2d(sa + j * 8192, &map_a, full, mb * BM + j * 64, kb * BK);
+                    }
+                    if (!g.b_mn) {
+                        tma_load_2d(sb, &map_b, full, kb * BK, nb * BN);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j)
+                            tma_load_2d(sb + j * 8192, &map_b, full, nb * BN + j * 64, kb * BK);
+                    }
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // -------------------------------- MMA issuer --------------------------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            int it = 0;
+            // per-K16 advance of the descriptor start address: 32 B inside a K-major row,
+            // two 8-row groups (2048 B) in an MN-major slab
+            const uint32_t a_step = g.a_mn ? 2048u : 32u, b_step = g.b_mn ? 2048u : 32u;
+            const uint32_t a_lbo = g.a_mn ? 8192u : 16u, b_lbo = g.b_mn ? 8192u : 16u;
+            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++it) {
+                const int acc = it & 1;
+                const uint32_t acc_phase = (it >> 1) & 1;
+                if (!mbar_wait_bounded(bar_tempty + 8 * acc, acc_phase ^ 1)) { atomicExch(g.err, 12); break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!mbar_wait_bounded(bar_full + 8 * stage, phase)) { atomicExch(g.err, 13); ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem_a + stage * kAStage);
+                    const uint32_t sb = smem_u32(smem_b + stage * kBStage);
+#pragma unroll
+                    for (int k16 = 0; k16 < BK / 16; ++k16) {
+                        const uint64_t ad = make_desc(sa + k16 * a_step, a_lbo, 1024);
+                        const uint64_t bd = make_desc(sb + k16 * b_step, b_lbo, 1024);
+                        tc_mma(d_tmem, ad, bd, g.idesc, (kb | k16) ? 1u : 0u);
+                    }
+                    tc_commit(bar_empty + 8 * stage);   // stage reusable once these MMAs have read it
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+                if (ok) tc_commit(bar_tfull + 8 * acc);  // accumulator complete
+            }
+        }
+    } else {
+        // --------------------------------- epilogue ---------------------------------
+        const int q = warp & 3;  // TMEM lane quarter this warp may address
+        int it = 0;
+        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++it) {
+            const int mb = tile / g.tiles_n, nb = tile % g.tiles_n;
+            const int acc = it & 1;
+            const uint32_t acc_phase = (it >> 1) & 1;
+            if (!mbar_wait_bounded(bar_tfull + 8 * acc, acc_phase)) { if (lane == 0) atomicExch(g.err, 14); break; }
+            tc_fence_after();
+            const int64_t row = (int64_t)mb * BM + q * 32 + lane;
+            const int64_t col_base = (int64_t)nb * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                const int64_t col0 = col_base + c * 32;
+                if (col0 >= g.N) break;
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, r);
+                tmem_ld_wait();
+                if (row < g.M) {
+                    if (g.c_dtype == SRU_BF16) epilogue_chunk<__nv_bfloat16>(g, r, row, col0);
+                    else if (g.c_dtype == SRU_F16) epilogue_chunk<__half>(g, r, row, col0);
+                    else epilogue_chunk<float>(g, r, row, col0);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+        }
+    }
+
+    // -------------------------------- teardown --------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ---- host side --------------------------------------------------------------------------
+PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(p);
+    }
+    return fn;
+}
+
+// 2-D tensor map over a row-major matrix: `inner` contiguous elements per row, `outer` rows,
+// row pitch ld elements; box = box_inner x box_outer; 128-byte swizzle; OOB reads give zeros.
+int make_map(CUtensorMap *map, const void *base, int dtype, int64_t inner, int64_t outer, int64_t ld,
+             int box_inner, int box_outer) {
+    auto fn = get_encode_fn();
+    if (!fn) return set_error(SRU_ERR_CUDA, "cuTensorMapEncodeTiled entry point not found");
+    cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, dtype == SRU_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                    const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(SRU_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    return 0;
+}
+
+}  // namespace
+
+}  // namespace srub
+
+using namespace srub;
+
+extern "C" int sru_b200_gemm(void *c, const void *a, const void *b, const float *col_bias, int64_t m, int64_t n,
+                             int64_t k_dim, int64_t lda, int64_t ldb, int64_t ldc, int trans_a, int trans_b,
+                             int ab_dtype, int c_dtype, int accumulate, void *stream) {
+    if (m < 0 || n < 0 || k_dim < 1) return set_error(SRU_ERR_BAD_ARG, "bad gemm sizes");
+    if (m == 0 || n == 0) return 0;
+    if (!c || !a || !b) return set_error(SRU_ERR_BAD_ARG, "gemm pointers must not be null");
+    if (ab_dtype != SRU_BF16 && ab_dtype != SRU_F16)
+        return set_error(SRU_ERR_UNSUPPORTED, "gemm operands must be bf16 or fp16");
+    if (c_dtype != SRU_BF16 && c_dtype != SRU_F16 && c_dtype != SRU_F32)
+        return set_error(SRU_ERR_UNSUPPORTED, "gemm output must be bf16, fp16 or fp32");
+    auto misaligned = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; };
+    if (misaligned(a) || misaligned(b) || misaligned(c) || (col_bias && misaligned(col_bias)))
+        return set_error(SRU_ERR_BAD_ARG, "gemm pointers must be 16-byte aligned");
+    if (lda % 8 || ldb % 8 || ldc % 8 || n % 8)
+        return set_error(SRU_ERR_BAD_ARG, "gemm leading dimensions and N must be multiples of 8 elements");
+    if (m > 0x7fffffff || n > 0x7fffffff || k_dim > 0x7fffffff) return set_error(SRU_ERR_BAD_ARG, "gemm size too large");
+
+    CUtensorMap map_a, map_b;
+    int rc;
+    // A: K-major stored (M,K) -> inner K, box 64 x 128.  MN-major stored (K,M) -> inner M, box 64 x 64.
+    if (!trans_a) rc = make_map(&map_a, a, ab_dtype, k_dim, m, lda, BK, BM);
+    else rc = make_map(&map_a, a, ab_dtype, m, k_dim, lda, 64, BK);
+    if (rc) return rc;
+    // B: K-major stored (N,K) -> inner K, box 64 x 256.  MN-major stored (K,N) -> inner N, box 64 x 64.
+    if (trans_b) rc = make_map(&map_b, b, ab_dtype, k_dim, n, ldb, BK, BN);
+    else rc = make_map(&map_b, b, ab_dtype, n, k_dim, ldb, 64, BK);
+    if (rc) return rc;
+
+    GemmArgs g;
+    g.c = c; g.bias = col_bias; g.M = m; g.N = n; g.K = k_dim; g.ldc = ldc;
+    g.c_dtype = c_dtype; g.accumulate = accumulate ? 1 : 0;
+    g.a_mn = trans_a ? 1 : 0;
+    g.b_mn = trans_b ? 0 : 1;
+    const uint32_t fmt = (ab_dtype == SRU_BF16) ? 1u : 0u;
+    // instruction descriptor: D fp32 (bits 4-5 = 1), A/B format (bits 7-9, 10-12), operand majors
+    // (bits 15, 16), N/8 (bits 17-22), M/16 (bits 24-28)
+    g.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)g.a_mn << 15) | ((uint32_t)g.b_mn << 16) |
+              ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+    g.tiles_m = (int)((m + BM - 1) / BM);
+    g.tiles_n = (int)((n + BN - 1) / BN);
+    g.err = device_error_flag();
+    if (!g.err) return set_error(SRU_ERR_CUDA, "device error flag unavailable");
+    const int64_t ntiles = (int64_t)g.tiles_m * g.tiles_n;
+    if (ntiles > 0x7fffffff) return set_error(SRU_ERR_BAD_ARG, "too many gemm tiles");
+
+    int dev = 0, sms = 148;
+    SRUB_CUDA_CHECK(cudaGetDevice(&dev));
+    SRUB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    static bool attr_set[64] = {false};
+    if (dev < 64 && !attr_set[dev]) {
+        SRUB_CUDA_CHECK(cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             kSmemBytes));
+        attr_set[dev] = true;
+    }
+    const unsigned grid = (unsigned)std::min<int64_t>(ntiles, sms);
+    gemm_tcgen05_kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(map_a, map_b, g);
+    SRUB_CUDA_CHECK(cudaGetLastError());
+    return 0;
 }

@@ -94,11 +94,12 @@ def scan_forward(u: Tensor, x: Optional[Tensor], weight_c: Tensor, bias: Optiona
             c_last.zero_()
         return h, c_hist, c_last
     with torch.cuda.device(u.device):
-        _lib.check(_lib.lib().sru_b200_scan_forward(
+        _lib.call(
+            "scan_fwd" if need_c_hist else "scan_fwd_infer", 1, _lib.lib().sru_b200_scan_forward,
             _lib.ptr(h), _lib.ptr(c_hist), _lib.ptr(c_last), _lib.ptr(u), _lib.ptr(x),
             _lib.ptr(weight_c), _lib.ptr(bias), _lib.ptr(c_init), _lib.ptr(mask_c), _lib.ptr(mask_pad),
             length, batch, d, dirs, k, activation_type, skip_type, is_custom, float(scale_x),
-            _lib.DTYPE_CODE[st], _lib.DTYPE_CODE[c_dtype], _lib.current_stream_ptr(u.device)))
+            _lib.DTYPE_CODE[st], _lib.DTYPE_CODE[c_dtype], _lib.current_stream_ptr(u.device))
     return h, c_hist, c_last
 
 
@@ -129,13 +130,14 @@ def scan_backward(u, x, weight_c, bias, c_init, mask_c, mask_pad, c_hist, grad_h
     nbytes = L.sru_b200_scan_backward_workspace_bytes(length, batch, d, dirs, k, code)
     workspace = torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=dev)
     with torch.cuda.device(dev):
-        _lib.check(L.sru_b200_scan_backward(
+        _lib.call(
+            "scan_bwd", 2, L.sru_b200_scan_backward,
             _lib.ptr(grad_u), _lib.ptr(grad_x), _lib.ptr(grad_wc), _lib.ptr(grad_bias), _lib.ptr(grad_init),
             _lib.ptr(u), _lib.ptr(x), _lib.ptr(weight_c), _lib.ptr(bias), _lib.ptr(c_init),
             _lib.ptr(mask_c), _lib.ptr(mask_pad), _lib.ptr(c_hist), _lib.ptr(grad_h), _lib.ptr(grad_last),
             length, batch, d, dirs, k, activation_type, skip_type, is_custom, float(scale_x),
             code, _lib.DTYPE_CODE[c_hist.dtype], _lib.ptr(workspace), workspace.numel(),
-            _lib.current_stream_ptr(dev)))
+            _lib.current_stream_ptr(dev))
     return grad_u, grad_x, grad_wc, grad_bias, grad_init
 
 

@@ -48,11 +48,13 @@ def gemm(a: Tensor, b: Tensor, trans_a: bool = False, trans_b: bool = False,
         return out if accumulate else out.zero_()
     bias = None if col_bias is None else col_bias.detach().float().contiguous()
     with torch.cuda.device(a.device):
-        _lib.check(_lib.lib().sru_b200_gemm(
+        name = "gemm_wgrad" if trans_a else ("gemm_dgrad" if trans_b else "gemm_fwd")
+        _lib.call(
+            name, 1, _lib.lib().sru_b200_gemm,
             _lib.ptr(out), _lib.ptr(a), _lib.ptr(b), _lib.ptr(bias), m, n, kd,
             a.stride(0), b.stride(0), out.stride(0), int(trans_a), int(trans_b),
             _lib.DTYPE_CODE[a.dtype], _lib.DTYPE_CODE[out.dtype], int(accumulate),
-            _lib.current_stream_ptr(a.device)))
+            _lib.current_stream_ptr(a.device))
     return out
 
 

@@ -1,0 +1,115 @@
+"""The tcgen05 GEMM (C ABI sru_b200_gemm) against an fp32 matmul of the same 16-bit operands.
+
+Tolerance: the products are exact in fp32 and accumulation is fp32 in tensor memory, so an fp32
+output must agree with a float32 library matmul to 1e-4 relative; a 16-bit output adds one
+rounding (bf16 2^-9, fp16 2^-11 relative), bound 1e-2 / 2e-3.  The 16-bit GEMM has no pinned
+result in the reference (it calls a vendor library), so the fp32 matmul is the checker here.
+"""
+import pytest
+import torch
+
+from conftest import rel_err
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _gemm():
+    from sru_b200.projection import gemm
+    return gemm
+
+
+def _ref(a, b, ta, tb):
+    A = a.float().t() if ta else a.float()
+    B = b.float().t() if tb else b.float()
+    return A @ B
+
+
+SIZES = [
+    # M,    N,    K
+    (128,  256,  64),
+    (256,  512,  128),
+    (640,  384,  128),      # first benchmark configuration's projection
+    (200,  264,  120),      # ragged M, N % 256 != 0, K % 64 != 0 (fbank-like input width 120)
+    (1000, 6144, 2048),     # one row block of the speech-style layer
+    (2048, 6144, 1000),     # weight-gradient shape: long reduction
+    (64,   8,    8),
+    (4096, 3072, 1024),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("layout", ["nn", "nt", "tn"])
+@pytest.mark.parametrize("size", SIZES)
+def test_gemm_layouts(size, layout, dtype):
+    """nn: U = x W (A K-major, B N-major); nt: grad_x = grad_U W^T; tn: grad_W = x^T grad_U."""
+    gemm = _gemm()
+    M, N, K = size
+    g = torch.Generator().manual_seed(M + N + K)
+    ta, tb = layout[0] == "t", layout[1] == "t"
+    a = (torch.randn((K, M) if ta else (M, K), generator=g) * 0.5).to(dtype).to(DEV)
+    b = (torch.randn((N, K) if tb else (K, N), generator=g) * 0.5).to(dtype).to(DEV)
+    ref = _ref(a, b, ta, tb)
+    out32 = gemm(a, b, trans_a=ta, trans_b=tb, out_dtype=torch.float32)
+    out16 = gemm(a, b, trans_a=ta, trans_b=tb)
+    torch.cuda.synchronize()
+    from sru_b200 import _lib
+    _lib.check_device_error()
+    assert out16.dtype == dtype and out32.dtype == torch.float32
+    assert rel_err(out32, ref) <= 1e-4, rel_err(out32, ref)
+    assert rel_err(out16, ref) <= (1e-2 if dtype == torch.bfloat16 else 2e-3), rel_err(out16, ref)
+
+
+def test_gemm_bias_and_accumulate():
+    gemm = _gemm()
+    g = torch.Generator().manual_seed(3)
+    M, N, K = 300, 520, 192
+    a = torch.randn(M, K, generator=g).bfloat16().to(DEV)
+    b = torch.randn(K, N, generator=g).bfloat16().to(DEV)
+    bias = torch.randn(N, generator=g).to(DEV)
+    ref = a.float() @ b.float()
+    out = gemm(a, b, out_dtype=torch.float32, col_bias=bias)
+    assert rel_err(out, ref + bias) <= 1e-4
+    base = torch.randn(M, N, generator=g).to(DEV)
+    acc = base.clone()
+    gemm(a, b, out=acc, accumulate=True)
+    assert rel_err(acc, ref + base) <= 1e-4
+    # strided output / operands: leading dimensions larger than the logical width
+    big_a = torch.zeros(M, K + 64, dtype=torch.bfloat16, device=DEV)
+    big_a[:, :K] = a
+    big_c = torch.full((M, N + 8), 7.0, device=DEV)
+    gemm(big_a[:, :K], b, out=big_c[:, :N])
+    assert rel_err(big_c[:, :N], ref) <= 1e-4
+    assert torch.all(big_c[:, N:] == 7.0)
+
+
+def test_gemm_many_tiles_persistent():
+    """More tiles than SMs: every CTA walks several tiles through both accumulators."""
+    gemm = _gemm()
+    g = torch.Generator().manual_seed(5)
+    M, N, K = 128 * 37, 256 * 9, 320
+    a = (torch.randn(M, K, generator=g) * 0.3).bfloat16().to(DEV)
+    b = (torch.randn(N, K, generator=g) * 0.3).bfloat16().to(DEV)
+    out = gemm(a, b, trans_b=True, out_dtype=torch.float32)
+    assert rel_err(out, a.float() @ b.float().t()) <= 1e-4
+
+
+def test_projection_autograd_matches_library():
+    """project() (tcgen05 forward / dgrad / wgrad) against torch.mm autograd on the same bf16 data."""
+    import os
+    from sru_b200.projection import project
+    os.environ["SRU_B200_GEMM"] = "tcgen05"
+    try:
+        g = torch.Generator().manual_seed(8)
+        x = torch.randn(384, 256, generator=g).bfloat16().to(DEV).requires_grad_(True)
+        w = (torch.randn(256, 768, generator=g) * 0.1).bfloat16().to(DEV).requires_grad_(True)
+        gu = torch.randn(384, 768, generator=g).bfloat16().to(DEV)
+        u = project(x, w)
+        u.backward(gu)
+        xr = x.detach().float().requires_grad_(True)
+        wr = w.detach().float().requires_grad_(True)
+        ur = xr @ wr
+        ur.backward(gu.float())
+        assert rel_err(u, ur) <= 1e-2 and rel_err(x.grad, xr.grad) <= 1e-2 and rel_err(w.grad, wr.grad) <= 1e-2
+    finally:
+        os.environ.pop("SRU_B200_GEMM", None)
