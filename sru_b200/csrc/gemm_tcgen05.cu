@@ -350,6 +350,11 @@ extern "C" int sru_b200_gemm(void *c, const void *a, const void *b, const float 
         return set_error(SRU_ERR_BAD_ARG, "gemm leading dimensions and N must be multiples of 8 elements");
     if (m > 0x7fffffff || n > 0x7fffffff || k_dim > 0x7fffffff) return set_error(SRU_ERR_BAD_ARG, "gemm size too large");
 
+    // The tensor-map encoder is a driver entry point and needs the device's primary context
+    // current on THIS thread; a thread that has only inherited a device ordinal (an autograd
+    // worker, for instance) gets it bound by this no-op runtime call.
+    SRUB_CUDA_CHECK(cudaFree(nullptr));
+
     CUtensorMap map_a, map_b;
     int rc;
     // A: K-major stored (M,K) -> inner K, box 64 x 128.  MN-major stored (K,M) -> inner M, box 64 x 64.

@@ -20,7 +20,13 @@ _SIXTEEN = (torch.float16, torch.bfloat16)
 
 def gemm_backend() -> str:
     """'tcgen05' (default) or 'library' (SRU_B200_GEMM=library forces torch.mm everywhere)."""
-    return os.environ.get("SRU_B200_GEMM", "library")
+    return os.environ.get("SRU_B200_GEMM", "tcgen05")
+
+
+def _tma_compatible(x: Tensor, w: Tensor) -> bool:
+    """The tensor-map loads need 16-byte aligned bases and row pitches (multiples of 8 elements)."""
+    return (x.size(1) % 8 == 0 and w.size(1) % 8 == 0 and x.size(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
 def gemm(a: Tensor, b: Tensor, trans_a: bool = False, trans_b: bool = False,
@@ -86,16 +92,19 @@ def project(x: Tensor, w: Tensor, col_bias: Optional[Tensor] = None) -> Tensor:
     if not x.is_cuda:
         raise _lib.SruB200Error("sru_b200 has no CPU path: the projection input must be a CUDA tensor")
     dt = x.dtype
-    if torch.is_autocast_enabled():
-        dt = torch.get_autocast_gpu_dtype()
+    if torch.is_autocast_enabled("cuda"):
+        dt = torch.get_autocast_dtype("cuda")
     elif w.dtype != x.dtype:
         dt = w.dtype
     if dt in _SIXTEEN and gemm_backend() == "tcgen05":
         xc = x if x.dtype == dt else x.to(dt)
         wc = w if w.dtype == dt else w.to(dt)
-        with torch.autocast("cuda", enabled=False):
-            return _Projection.apply(xc, wc, col_bias)
-    out = x.mm(w) if x.dtype == w.dtype or torch.is_autocast_enabled() else x.to(dt).mm(w)
+        xc = xc if xc.is_contiguous() else xc.contiguous()
+        wc = wc if wc.is_contiguous() else wc.contiguous()
+        if _tma_compatible(xc, wc):
+            with torch.autocast("cuda", enabled=False):
+                return _Projection.apply(xc, wc, col_bias)
+    out = x.mm(w) if x.dtype == w.dtype or torch.is_autocast_enabled("cuda") else x.to(dt).mm(w)
     if col_bias is not None:
         out = out + col_bias.to(out.dtype)
     return out
