@@ -123,6 +123,40 @@ int sru_b200_scan_backward(
     int dtype, int c_dtype, void *workspace, size_t workspace_bytes, void *stream);
 
 /*
+ * Backward scan that allocates nothing and takes no workspace argument.  It has no
+ * counterpart in the reference (whose operators allocate their outputs and scratch
+ * themselves); it exists for hosts that must not, or cannot, allocate device memory
+ * around the call: a serving loop with a fixed memory plan, a plugin sandbox without
+ * an allocator, a section of a stream in which allocation calls are forbidden.
+ *
+ * Arguments, results and kernels are those of sru_b200_scan_backward; the scratch is a
+ * fixed array inside the library, sru_b200_scan_backward_noalloc_max_bytes() bytes
+ * (8 MiB) on every GPU that has loaded the library, held until the process exits.
+ *
+ *   - Limit: the problem must satisfy
+ *       sru_b200_scan_backward_workspace_bytes(...) <= ..._noalloc_max_bytes(),
+ *     i.e. batch * dirs * hidden <= 524288 (262144 for SRU_F64); larger problems get
+ *     SRU_ERR_WORKSPACE and a message naming both sizes.
+ *   - The first call on each device resolves the array's device address (that device
+ *     must be current).  Make that first call before any stream capture begins.
+ *   - All calls on a device share the one array.  Nothing in it needs clearing between
+ *     calls, but two calls whose kernels overlap on the GPU (different streams without
+ *     an ordering between them) race on it: keep calls on one device stream-ordered.
+ *   - No cudaMalloc / cudaFree, no allocating library routine, inputs and outputs are
+ *     still the caller's.
+ */
+size_t sru_b200_scan_backward_noalloc_max_bytes(void);
+
+int sru_b200_scan_backward_noalloc(
+    void *grad_u, void *grad_x, void *grad_wc, void *grad_bias, void *grad_init,
+    const void *u, const void *x, const void *weight_c, const void *bias,
+    const void *c_init, const void *mask_c, const uint8_t *mask_pad,
+    const void *c_hist, const void *grad_h, const void *grad_last,
+    int64_t length, int64_t batch, int64_t hidden, int dirs, int k,
+    int activation_type, int skip_type, int is_custom, double scale_x,
+    int dtype, int c_dtype, void *stream);
+
+/*
  * Dense contraction on the tcgen05 tensor cores, the replacement for the three
  * library GEMMs around the scan: U = x * W of SRUCell.compute_U
  * (sru/modules.py:363-378) and, in backward, grad_x = grad_U * W^T and
