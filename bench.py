@@ -238,8 +238,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-batch", type=int, default=0)
+    ap.add_argument("--batch", type=int, default=0,
+                    help="override the global batch (profiling on a small case; the workload name says so)")
     args = ap.parse_args()
-    cfg = CONFIGS[args.config]
+    cfg = dict(CONFIGS[args.config])
+    if args.batch:
+        cfg["name"] = cfg["name"] + " [batch reduced to %d]" % args.batch
+        cfg["B"] = args.batch
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

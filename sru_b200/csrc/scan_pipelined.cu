@@ -134,7 +134,7 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const PipeArgs p) {
     const int r = tid / TPR;
     const int hc = (tid - r * TPR) * V;
     const bool active = (tid < BR * TPR) && (r < nrows);
-    const int64_t b = b0 + r;
+    const int64_t b = b0 + (active ? r : 0);
     const int64_t col = b * D + dj0 + hc;
     const bool has_pad = a.mask_pad != nullptr;
 
@@ -157,77 +157,84 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const PipeArgs p) {
         }
     }
     const float scale = (float)a.scale_x;
-    T *h = (T *)a.h;
-    TC *ch = (TC *)a.c_hist;
+    // Running pointers: one add per time step instead of rebuilding (t*B + b)*D + ... each step.
+    const int64_t t_first = dir ? (L - 1) : 0;
+    const int64_t ostep = dir ? -(a.B * D) : (a.B * D);
+    T *hp = (T *)a.h + (t_first * a.B + b) * D + dj0 + hc;
+    const bool has_hist = a.c_hist != nullptr;
+    TC *cp = (TC *)a.c_hist + (has_hist ? (t_first * a.B + b) * D + dj0 + hc : 0);
+    const int64_t pstep = dir ? -a.B : a.B;
+    const uint8_t *pp = has_pad ? a.mask_pad + t_first * a.B + b : nullptr;
+    const uint32_t su = BR * u_slab, sx = BR * x_slab;
+    const uint32_t u_off = r * u_slab + hc * K * sizeof(T);
+    const uint32_t x_off = u_region + r * x_slab + hc * sizeof(T);
 
-    auto load_pad = [&](int it) -> uint32_t {
+    // pad flags of scan steps n_first .. n_first+kTS-1, one bit each; fetched two stages ahead
+    auto load_pad = [&](int64_t n_first) -> uint32_t {
         uint32_t bits = 0;
         if (has_pad && active) {
+            const uint8_t *q = pp + n_first * pstep;
 #pragma unroll
-            for (int ts = 0; ts < kTS; ++ts) {
-                const int64_t n = (int64_t)it * kTS + ts;
-                if (n < L) {
-                    const int64_t t = dir ? (L - 1 - n) : n;
-                    bits |= (a.mask_pad[t * a.B + b] ? 1u : 0u) << ts;
-                }
-            }
+            for (int ts = 0; ts < kTS; ++ts)
+                if (n_first + ts < L) bits |= (q[ts * pstep] ? 1u : 0u) << ts;
         }
         return bits;
     };
-    uint32_t pad_next = load_pad(0);
+    uint32_t pad0 = load_pad(0), pad1 = load_pad(kTS);
 
+    int s = 0;
+    uint32_t ph = 0;
     for (int it = 0; it < nst; ++it) {
-        const int s = it % NS;
-        if (!mbar_wait_bounded(bar_full + 8 * s, (it / NS) & 1)) {
+        if (!mbar_wait_bounded(bar_full + 8 * s, ph)) {
             atomicExch(p.err, 2);
             break;
         }
-        const uint32_t pad_cur = pad_next;
-        pad_next = load_pad(it + 1);
+        const uint32_t pad_cur = pad0;
+        pad0 = pad1;
+        pad1 = load_pad((int64_t)(it + 2) * kTS);
         const uint8_t *sb = stage0 + (size_t)s * stage_bytes;
-        const int64_t n0 = (int64_t)it * kTS;
+        const int steps = (int)min((int64_t)kTS, L - (int64_t)it * kTS);
+        if (active) {
 #pragma unroll
-        for (int ts = 0; ts < kTS; ++ts) {
-            const int64_t n = n0 + ts;
-            if (n < L && active) {
-                const int64_t t = dir ? (L - 1 - n) : n;
-                const int64_t o = (t * a.B + b) * D + dj0 + hc;
-                Pack<T, V> ho;
-                if (!((pad_cur >> ts) & 1u)) {
-                    const Pack<T, V * K> up = *reinterpret_cast<const Pack<T, V * K> *>(
-                        sb + (size_t)(ts * BR + r) * u_slab + (size_t)hc * K * sizeof(T));
-                    Pack<T, V> xp;
-                    if (has_x)
-                        xp = *reinterpret_cast<const Pack<T, V> *>(
-                            sb + u_region + (size_t)(ts * BR + r) * x_slab + (size_t)hc * sizeof(T));
+            for (int ts = 0; ts < kTS; ++ts) {
+                if (ts < steps) {
+                    Pack<T, V> ho;
+                    if (!((pad_cur >> ts) & 1u)) {
+                        const Pack<T, V * K> up = *reinterpret_cast<const Pack<T, V * K> *>(sb + u_off + ts * su);
+                        Pack<T, V> xp;
+                        if (has_x) xp = *reinterpret_cast<const Pack<T, V> *>(sb + x_off + ts * sx);
 #pragma unroll
-                    for (int i = 0; i < V; ++i) {
-                        const float u0 = Cvt<T>::to_f(up.v[i * K + 0]);
-                        const float u1 = Cvt<T>::to_f(up.v[i * K + 1]);
-                        const float u2 = Cvt<T>::to_f(up.v[i * K + 2]);
-                        float xv = 0.f;
-                        if (K == 4) xv = Cvt<T>::to_f(up.v[i * K + K - 1]);
-                        else if (has_x) xv = Cvt<T>::to_f(xp.v[i]) * scale;
-                        const float g1 = G::eval(c[i], wc1n[i], u1, b1n[i]);
-                        const float g2 = G::eval(c[i], wc2n[i], u2, b2n[i]);
-                        c[i] = fmaf(c[i] - u0, g1, u0);
-                        ho.v[i] = Cvt<T>::from_f(fmaf((c[i] - xv) * mk[i], g2, xv));
+                        for (int i = 0; i < V; ++i) {
+                            const float u0 = Cvt<T>::to_f(up.v[i * K + 0]);
+                            const float u1 = Cvt<T>::to_f(up.v[i * K + 1]);
+                            const float u2 = Cvt<T>::to_f(up.v[i * K + 2]);
+                            float xv = 0.f;
+                            if (K == 4) xv = Cvt<T>::to_f(up.v[i * K + K - 1]);
+                            else if (has_x) xv = Cvt<T>::to_f(xp.v[i]) * scale;
+                            const float g1 = G::eval(c[i], wc1n[i], u1, b1n[i]);
+                            const float g2 = G::eval(c[i], wc2n[i], u2, b2n[i]);
+                            c[i] = fmaf(c[i] - u0, g1, u0);
+                            ho.v[i] = Cvt<T>::from_f(fmaf((c[i] - xv) * mk[i], g2, xv));
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < V; ++i) ho.v[i] = Cvt<T>::from_f(0.f);
                     }
-                } else {
+                    *reinterpret_cast<Pack<T, V> *>(hp) = ho;
+                    hp += ostep;
+                    if (has_hist) {
+                        Pack<TC, V> co;
 #pragma unroll
-                    for (int i = 0; i < V; ++i) ho.v[i] = Cvt<T>::from_f(0.f);
-                }
-                *reinterpret_cast<Pack<T, V> *>(h + o) = ho;
-                if (ch) {
-                    Pack<TC, V> co;
-#pragma unroll
-                    for (int i = 0; i < V; ++i) co.v[i] = Cvt<TC>::from_f(c[i]);
-                    *reinterpret_cast<Pack<TC, V> *>(ch + o) = co;
+                        for (int i = 0; i < V; ++i) co.v[i] = Cvt<TC>::from_f(c[i]);
+                        *reinterpret_cast<Pack<TC, V> *>(cp) = co;
+                        cp += ostep;
+                    }
                 }
             }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_empty + 8 * s);
+        if (++s == NS) { s = 0; ph ^= 1; }
     }
     if (a.c_last && active) {
         Pack<float, V> cl;
@@ -343,7 +350,7 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const PipeArgs p) {
         }
     } else {
         // -------------------------------- consumers --------------------------------
-        const int64_t b = b0 + r;
+        const int64_t b = b0 + (active ? r : 0);
         const int64_t col = b * D + dj0 + hc;
         const bool has_pad = a.mask_pad != nullptr;
         float cur[V], wc1n[V], wc2n[V], b1n[V], b2n[V], mk[V], c0[V];
@@ -366,101 +373,107 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const PipeArgs p) {
             }
         }
         const float scale = (float)a.scale_x;
-        T *gu = (T *)a.grad_u;
-        T *gx = (T *)a.grad_x;
+        // Backward step m visits the forward's scan step n = L-1-m, i.e. time t = dir ? m : L-1-m.
+        const int64_t t_first = dir ? 0 : (L - 1);
+        const int64_t ostep = dir ? (a.B * D) : -(a.B * D);
+        const int64_t o_first = (t_first * a.B + b) * D + dj0 + hc;
+        T *gup = (T *)a.grad_u + o_first * K;
+        T *gxp = (T *)a.grad_x + (has_x ? o_first : 0);
+        const int64_t pstep = dir ? a.B : -a.B;
+        const uint8_t *pp = has_pad ? a.mask_pad + t_first * a.B + b : nullptr;
+        const uint32_t su = BR * u_slab, sx = BR * x_slab, sc = BR * c_slab, sg = BR * g_slab;
+        const uint32_t u_off = r * u_slab + hc * K * sizeof(T);
+        const uint32_t x_off = u_region + r * x_slab + hc * sizeof(T);
+        const uint32_t c_off = u_region + x_region + r * c_slab + hc * sizeof(TC);
+        const uint32_t g_off = u_region + x_region + c_region + r * g_slab + hc * sizeof(T);
 
-        auto load_pad = [&](int it) -> uint32_t {
+        auto load_pad = [&](int64_t m_first) -> uint32_t {
             uint32_t bits = 0;
             if (has_pad && active) {
+                const uint8_t *q = pp + m_first * pstep;
 #pragma unroll
-                for (int ts = 0; ts < kTS; ++ts) {
-                    const int64_t m = (int64_t)it * kTS + ts;
-                    if (m < L) {
-                        const int64_t n = L - 1 - m;
-                        const int64_t t = dir ? (L - 1 - n) : n;
-                        bits |= (a.mask_pad[t * a.B + b] ? 1u : 0u) << ts;
-                    }
-                }
+                for (int ts = 0; ts < kTS; ++ts)
+                    if (m_first + ts < L) bits |= (q[ts * pstep] ? 1u : 0u) << ts;
             }
             return bits;
         };
-        uint32_t pad_next = load_pad(0);
+        uint32_t pad0 = load_pad(0), pad1 = load_pad(kTS);
 
+        int s = 0;
+        uint32_t ph = 0;
         for (int it = 0; it < nst; ++it) {
-            const int s = it % NS;
-            if (!mbar_wait_bounded(bar_full + 8 * s, (it / NS) & 1)) {
+            if (!mbar_wait_bounded(bar_full + 8 * s, ph)) {
                 atomicExch(p.err, 4);
                 break;
             }
-            const uint32_t pad_cur = pad_next;
-            pad_next = load_pad(it + 1);
+            const uint32_t pad_cur = pad0;
+            pad0 = pad1;
+            pad1 = load_pad((int64_t)(it + 2) * kTS);
             const uint8_t *sb = stage0 + (size_t)s * stage_bytes;
-            const int64_t m0 = (int64_t)it * kTS;
+            const int64_t left = L - (int64_t)it * kTS;   // steps left including this stage
+            const int steps = (int)min((int64_t)kTS, left);
+            if (active) {
 #pragma unroll
-            for (int ts = 0; ts < kTS; ++ts) {
-                const int64_t m = m0 + ts;
-                if (m < L && active) {
-                    const int64_t n = L - 1 - m;
-                    const int64_t t = dir ? (L - 1 - n) : n;
-                    const int64_t o = (t * a.B + b) * D + dj0 + hc;
-                    Pack<T, V * K> guo;
-                    Pack<T, V> gxo;
-                    if (!((pad_cur >> ts) & 1u)) {
-                        const size_t srow = (size_t)(ts * BR + r);
-                        const Pack<T, V * K> up = *reinterpret_cast<const Pack<T, V * K> *>(
-                            sb + srow * u_slab + (size_t)hc * K * sizeof(T));
-                        const Pack<T, V> ghp = *reinterpret_cast<const Pack<T, V> *>(
-                            sb + u_region + x_region + c_region + srow * g_slab + (size_t)hc * sizeof(T));
-                        Pack<T, V> xp;
-                        if (has_x)
-                            xp = *reinterpret_cast<const Pack<T, V> *>(
-                                sb + u_region + srow * x_slab + (size_t)hc * sizeof(T));
-                        Pack<TC, V> cpp;
-                        if (n > 0)
-                            cpp = *reinterpret_cast<const Pack<TC, V> *>(
-                                sb + u_region + x_region + srow * c_slab + (size_t)hc * sizeof(TC));
+                for (int ts = 0; ts < kTS; ++ts) {
+                    if (ts < steps) {
+                        Pack<T, V * K> guo;
+                        Pack<T, V> gxo;
+                        if (!((pad_cur >> ts) & 1u)) {
+                            const bool at_start = (ts == left - 1);   // n == 0: the state before it is c_init
+                            const Pack<T, V * K> up = *reinterpret_cast<const Pack<T, V * K> *>(sb + u_off + ts * su);
+                            const Pack<T, V> ghp = *reinterpret_cast<const Pack<T, V> *>(sb + g_off + ts * sg);
+                            Pack<T, V> xp;
+                            if (has_x) xp = *reinterpret_cast<const Pack<T, V> *>(sb + x_off + ts * sx);
+                            Pack<TC, V> cpp;
+                            if (!at_start) cpp = *reinterpret_cast<const Pack<TC, V> *>(sb + c_off + ts * sc);
 #pragma unroll
-                        for (int i = 0; i < V; ++i) {
-                            const float u0 = Cvt<T>::to_f(up.v[i * K + 0]);
-                            const float u1 = Cvt<T>::to_f(up.v[i * K + 1]);
-                            const float u2 = Cvt<T>::to_f(up.v[i * K + 2]);
-                            float xv = 0.f;
-                            if (K == 4) xv = Cvt<T>::to_f(up.v[i * K + K - 1]);
-                            else if (has_x) xv = Cvt<T>::to_f(xp.v[i]) * scale;
-                            const float cp = (n > 0) ? Cvt<TC>::to_f(cpp.v[i]) : c0[i];
-                            const float gh = Cvt<T>::to_f(ghp.v[i]);
-                            const float g1 = G::eval(cp, wc1n[i], u1, b1n[i]);
-                            const float g2 = G::eval(cp, wc2n[i], u2, b2n[i]);
-                            const float dc = cp - u0;
-                            const float cv = fmaf(dc, g1, u0);
-                            const float ghm = gh * mk[i];
-                            const float gg2 = ghm * (cv - xv) * (g2 - g2 * g2);
-                            const float gc = fmaf(ghm, g2, cur[i]);
-                            const float gg1 = gc * dc * (g1 - g1 * g1);
-                            gb1[i] += gg1;
-                            gb2[i] += gg2;
-                            gwc1[i] = fmaf(gg1, cp, gwc1[i]);
-                            gwc2[i] = fmaf(gg2, cp, gwc2[i]);
-                            cur[i] = fmaf(gc, g1, G::kUnfold * fmaf(gg1, wc1n[i], gg2 * wc2n[i]));
-                            const float gxv = fmaf(-ghm, g2, gh);
-                            guo.v[i * K + 0] = Cvt<T>::from_f(fmaf(-gc, g1, gc));
-                            guo.v[i * K + 1] = Cvt<T>::from_f(gg1);
-                            guo.v[i * K + 2] = Cvt<T>::from_f(gg2);
-                            if (K == 4) guo.v[i * K + K - 1] = Cvt<T>::from_f(gxv);
-                            gxo.v[i] = Cvt<T>::from_f(gxv * scale);
+                            for (int i = 0; i < V; ++i) {
+                                const float u0 = Cvt<T>::to_f(up.v[i * K + 0]);
+                                const float u1 = Cvt<T>::to_f(up.v[i * K + 1]);
+                                const float u2 = Cvt<T>::to_f(up.v[i * K + 2]);
+                                float xv = 0.f;
+                                if (K == 4) xv = Cvt<T>::to_f(up.v[i * K + K - 1]);
+                                else if (has_x) xv = Cvt<T>::to_f(xp.v[i]) * scale;
+                                const float cp = at_start ? c0[i] : Cvt<TC>::to_f(cpp.v[i]);
+                                const float gh = Cvt<T>::to_f(ghp.v[i]);
+                                const float g1 = G::eval(cp, wc1n[i], u1, b1n[i]);
+                                const float g2 = G::eval(cp, wc2n[i], u2, b2n[i]);
+                                const float dc = cp - u0;
+                                const float cv = fmaf(dc, g1, u0);
+                                const float ghm = gh * mk[i];
+                                const float gg2 = ghm * (cv - xv) * (g2 - g2 * g2);
+                                const float gc = fmaf(ghm, g2, cur[i]);
+                                const float gg1 = gc * dc * (g1 - g1 * g1);
+                                gb1[i] += gg1;
+                                gb2[i] += gg2;
+                                gwc1[i] = fmaf(gg1, cp, gwc1[i]);
+                                gwc2[i] = fmaf(gg2, cp, gwc2[i]);
+                                cur[i] = fmaf(gc, g1, G::kUnfold * fmaf(gg1, wc1n[i], gg2 * wc2n[i]));
+                                const float gxv = fmaf(-ghm, g2, gh);
+                                guo.v[i * K + 0] = Cvt<T>::from_f(fmaf(-gc, g1, gc));
+                                guo.v[i * K + 1] = Cvt<T>::from_f(gg1);
+                                guo.v[i * K + 2] = Cvt<T>::from_f(gg2);
+                                if (K == 4) guo.v[i * K + K - 1] = Cvt<T>::from_f(gxv);
+                                gxo.v[i] = Cvt<T>::from_f(gxv * scale);
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < V * K; ++i) guo.v[i] = Cvt<T>::from_f(0.f);
+#pragma unroll
+                            for (int i = 0; i < V; ++i) gxo.v[i] = Cvt<T>::from_f(0.f);
                         }
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < V * K; ++i) guo.v[i] = Cvt<T>::from_f(0.f);
-#pragma unroll
-                        for (int i = 0; i < V; ++i) gxo.v[i] = Cvt<T>::from_f(0.f);
+                        *reinterpret_cast<Pack<T, V * K> *>(gup) = guo;
+                        gup += ostep * K;
+                        if (has_x) {
+                            *reinterpret_cast<Pack<T, V> *>(gxp) = gxo;
+                            gxp += ostep;
+                        }
                     }
-                    *reinterpret_cast<Pack<T, V * K> *>(gu + o * K) = guo;
-                    if (has_x) *reinterpret_cast<Pack<T, V> *>(gx + o) = gxo;
                 }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty + 8 * s);
+            if (++s == NS) { s = 0; ph ^= 1; }
         }
         if (active) {
             Pack<float, V> gi;
@@ -524,16 +537,14 @@ static bool choose_tile(int64_t L, int64_t B, int64_t d, int dirs, int k, int sk
     const int64_t D = d * dirs, ncols = B * D;
     const int sms = num_sms();
     const int vmax = granule, vmin = (s == 2) ? 2 : 1;
-    // widest V that still gives every SM sub-partition a warp
-    int v = vmin;
-    for (int cand = vmax; cand >= vmin; cand /= 2) {
-        if (ncols / (32 * cand) >= (int64_t)sms * 4) { v = cand; break; }
-    }
+    // Columns per thread.  Measured on B200: with three or more warps per SM available, V = 4
+    // amortises the per-step overhead best (V = 8 costs registers and occupancy for nothing);
+    // smaller problems are bound by per-step latency and want as many warps as possible.
+    int v = (ncols / (32 * 4) >= (int64_t)sms * 3 && vmax >= 4) ? 4 : vmin;
     v = env_int(backward ? "SRU_B200_BWD_V" : "SRU_B200_FWD_V", v);
     if (v < vmin || v > vmax || (v & (v - 1))) return false;
-    // consumer threads per CTA: enough CTAs for two per SM when the problem allows
-    int ntc = 128;
-    while (ntc > 32 && ncols / ((int64_t)v * ntc) < (int64_t)sms * 2) ntc /= 2;
+    // consumer threads per CTA: two warps, one when that is needed to give every SM a CTA
+    int ntc = (ncols / ((int64_t)v * 64) >= (int64_t)sms) ? 64 : 32;
     ntc = env_int("SRU_B200_SCAN_THREADS", ntc);
     if (ntc < 32 || ntc > 128 || ntc % 32) return false;
     // hidden width of the tile: largest divisor of d, multiple of the granule, <= v*ntc

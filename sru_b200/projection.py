@@ -31,7 +31,7 @@ def _tma_compatible(x: Tensor, w: Tensor) -> bool:
 
 def gemm(a: Tensor, b: Tensor, trans_a: bool = False, trans_b: bool = False,
          out_dtype: Optional[torch.dtype] = None, col_bias: Optional[Tensor] = None,
-         out: Optional[Tensor] = None, accumulate: bool = False) -> Tensor:
+         out: Optional[Tensor] = None, accumulate: bool = False, name: Optional[str] = None) -> Tensor:
     """C = op(a) @ op(b) (+ col_bias) on the tcgen05 kernel.  a, b: 2-D, 16-bit, same dtype,
     unit stride in the last dimension.  op(a) is M x K, op(b) is K x N."""
     if a.dtype not in _SIXTEEN or b.dtype != a.dtype:
@@ -54,7 +54,8 @@ def gemm(a: Tensor, b: Tensor, trans_a: bool = False, trans_b: bool = False,
         return out if accumulate else out.zero_()
     bias = None if col_bias is None else col_bias.detach().float().contiguous()
     with torch.cuda.device(a.device):
-        name = "gemm_wgrad" if trans_a else ("gemm_dgrad" if trans_b else "gemm_fwd")
+        if name is None:
+            name = "gemm_wgrad" if trans_a else ("gemm_dgrad" if trans_b else "gemm_fwd")
         _lib.call(
             name, 1, _lib.lib().sru_b200_gemm,
             _lib.ptr(out), _lib.ptr(a), _lib.ptr(b), _lib.ptr(bias), m, n, kd,
@@ -70,6 +71,10 @@ class _Projection(Function):
         # x (M, K), w (K, N), both already in the 16-bit compute dtype
         ctx.save_for_backward(x, w)
         ctx.has_bias = col_bias is not None
+        if x.size(0) >= 4 * w.size(0):
+            # Many more rows than weights: a K-major copy of W (a few MB, made once per call)
+            # lets both operands stream as K-major tiles, the fastest operand form of the kernel.
+            return gemm(x, w.t().contiguous(), trans_b=True, col_bias=col_bias, name="gemm_fwd")
         return gemm(x, w, col_bias=col_bias)
 
     @staticmethod
