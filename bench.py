@@ -240,8 +240,15 @@ def main():
     ap.add_argument("--cpu-sample-batch", type=int, default=0)
     ap.add_argument("--batch", type=int, default=0,
                     help="override the global batch (profiling on a small case; the workload name says so)")
+    ap.add_argument("--length", type=int, default=0,
+                    help="override the sequence length (profiling on a small case; the workload name says so)")
     args = ap.parse_args()
     cfg = dict(CONFIGS[args.config])
+    if args.length:
+        cfg["name"] = cfg["name"] + " [length reduced to %d]" % args.length
+        if cfg["lens"] is not None:
+            cfg["lens"] = (max(1, cfg["lens"][0] * args.length // cfg["L"]), args.length)
+        cfg["L"] = args.length
     if args.batch:
         cfg["name"] = cfg["name"] + " [batch reduced to %d]" % args.batch
         cfg["B"] = args.batch

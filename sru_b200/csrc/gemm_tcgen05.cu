@@ -23,7 +23,7 @@
 // and none of them needs a transposed copy.  Shared-memory tiles are the canonical 128-byte
 // swizzled layouts: K-major [rows][64 elements], 8-row groups 1024 B apart; MN-major slabs of
 // [64 k-rows][64 elements], 8-row groups 1024 B apart, successive 64-element chunks of the
-// M / N extent 8192 B apart.  No load uses cluster multicast.
+// M / N extent 8192 B apart.  Every load is issued by one CTA for its own shared memory.
 //
 // Every mbarrier wait is bounded; a wait that gives up raises the device error flag and the
 // CTA drains to its teardown, where tensor memory is released.

@@ -10,11 +10,18 @@
 // HW) elements per row.  One extra warp, the producer, streams them kTS time steps at a
 // time into a ring of NS shared-memory stages with untiled bulk asynchronous copies
 // (cp.async.bulk, completion counted on an mbarrier per stage); consumers wait on the
-// stage's "full" barrier, read their 4..48-byte slices with vector shared loads, and
+// stage's "full" barrier, read their 2..48-byte slices with vector shared loads, and
 // release the stage through its "empty" barrier.  The depth in time of the ring, not the
 // number of resident threads, provides the bytes in flight that HBM needs.  Outputs go
 // straight from registers to global memory with V*sizeof(T)-byte stores that are
 // contiguous across the warp.
+//
+// Latency.  Small problems leave about one warp per SM sub-partition, so what bounds them is
+// the dependent-instruction latency of one time step.  The body of a stage is therefore
+// branch-free (padding and the c_init boundary are selects, the options are template
+// parameters) and unrolled over the kTS steps of the stage, which lets the scheduler overlap
+// the loads, conversions and output arithmetic of neighbouring steps with the one chain that
+// is truly serial: c' -> gate -> c.
 //
 // Every wait is bounded (mbar_wait_bounded); on a timeout the thread raises the device
 // error flag, stops processing and falls through to the end of the kernel.
@@ -22,9 +29,9 @@
 // Arithmetic (same as the reference kernels sru/csrc/sru_cuda_kernel.cu:60-78 forward,
 // :130-176 backward, with the direction taken from the tile instead of col % 2d):
 //   g1 = s(u1 + wc1*c' + b1), g2 = s(u2 + wc2*c' + b2), c = (c' - u0)*g1 + u0,
-//   h = (c - x')*m*g2 + x',  x' = x*scale_x (k=3) | u3 (k=4) | 0,
-// where s(z) = 1/(1 + 2^(-z*log2 e)) is evaluated with ex2.approx / rcp.approx and the
-// -log2 e factor is folded into wc and b once per column.
+//   h = (c - x')*m*g2 + x',  x' = x*scale_x (k=3) | u3 (k=4).
+#include <type_traits>
+
 #include "scan.cuh"
 
 namespace srub {
@@ -39,34 +46,89 @@ struct PipeArgs {
     int *err;
 };
 
-// Gate evaluation.  ACC (fp32 storage): the reference's own expression 1/(1+expf(-z)) with
-// full-precision expf and IEEE division, so fp32 results stay within 1e-5 of an fp32 CPU run
-// over long sequences.  !ACC (16-bit storage): -log2(e) folded into wc and b once per column,
-// then ex2.approx + rcp.approx (two MUFU operations per gate).
-template <bool ACC> struct Gate {
-    static __device__ __forceinline__ float fold(float v) { return ACC ? v : v * kNegLog2e; }
+__device__ __forceinline__ float tanh_approx(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Gate evaluation s(u + wc*c + b).
+//  MODE 0 (fp32 storage): the reference's own expression 1/(1+expf(-z)) with full-precision
+//         expf and IEEE division, so fp32 results stay within 1e-5 of an fp32 CPU run.
+//  MODE 1: -log2(e) folded into wc and b once per column, ex2.approx + rcp.approx.
+//  MODE 2 (16-bit storage): s(z) = 0.5*tanh(z/2) + 0.5 with 1/2 folded into wc and b and one
+//         tanh.approx per gate: half the special-function work and the shortest serial chain
+//         (fma -> tanh -> fma).  Its absolute error (about 3e-4) is below bf16 / fp16 output
+//         rounding and inside the 2e-2 bar of the 16-bit modes.
+template <int MODE> struct Gate {
+    static __device__ __forceinline__ float fold(float v) {
+        return MODE == 0 ? v : (MODE == 1 ? v * kNegLog2e : v * 0.5f);
+    }
     // multiplies (gg1*wc1f + gg2*wc2f) back to (gg1*wc1 + gg2*wc2)
-    static constexpr float kUnfold = ACC ? 1.f : -0.6931471805599453f;
+    static constexpr float kUnfold = MODE == 0 ? 1.f : (MODE == 1 ? -0.6931471805599453f : 2.f);
     static __device__ __forceinline__ float eval(float c, float wcf, float u, float bf) {
-        if (ACC) {
+        if (MODE == 0) {
             const float z = fmaf(wcf, c, u) + bf;
             return 1.f / (1.f + expf(-z));
-        } else {
+        } else if (MODE == 1) {
             return rcp_approx(1.f + ex2_approx(fmaf(c, wcf, fmaf(u, kNegLog2e, bf))));
+        } else {
+            return fmaf(tanh_approx(fmaf(c, wcf, fmaf(u, 0.5f, bf))), 0.5f, 0.5f);
         }
     }
 };
+template <typename T> using GateFor = Gate<sizeof(T) == 4 ? 0 : 2>;
+
+// float[N] -> Pack<T,N>, two values per conversion instruction for the 16-bit types.
+template <typename T, int N> __device__ __forceinline__ void pack_from_float(Pack<T, N> &out, const float (&v)[N]) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) out.v[i] = Cvt<T>::from_f(v[i]);
+}
+template <int N> __device__ __forceinline__ void pack_from_float(Pack<__nv_bfloat16, N> &out, const float (&v)[N]) {
+    if constexpr (N % 2 == 0) {
+#pragma unroll
+        for (int i = 0; i < N; i += 2)
+            *reinterpret_cast<__nv_bfloat162 *>(&out.v[i]) = __floats2bfloat162_rn(v[i], v[i + 1]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) out.v[i] = __float2bfloat16_rn(v[i]);
+    }
+}
+template <int N> __device__ __forceinline__ void pack_from_float(Pack<__half, N> &out, const float (&v)[N]) {
+    if constexpr (N % 2 == 0) {
+#pragma unroll
+        for (int i = 0; i < N; i += 2) *reinterpret_cast<__half2 *>(&out.v[i]) = __floats2half2_rn(v[i], v[i + 1]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) out.v[i] = __float2half_rn(v[i]);
+    }
+}
+
+// A producer lane's copy slot: a fixed (time step within the stage, tile row, tensor); its global
+// source advances by a constant number of bytes from one stage to the next, so the per-stage
+// work of the producer is a wait, one expect_tx and a few address additions (no index decoding).
+struct CopySlot {
+    const uint8_t *src;
+    int64_t stage_step;   // bytes added to src per stage
+    uint32_t dst_off;     // byte offset inside a stage
+    uint32_t bytes;
+    int ts;               // time step within the stage; >= kTS marks an unused slot
+    int is_cprev;         // backward: the c[t-1] slab, absent for the step whose predecessor is c_init
+};
+constexpr int kSlotsPerLane = 4;
+
+template <bool B> using BoolC = std::integral_constant<bool, B>;
 
 template <typename T, typename TC, int V, int K>
 __global__ void __launch_bounds__(160) scan_fwd_pipe(const PipeArgs p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    using G = Gate<sizeof(T) == 4>;
+    using G = GateFor<T>;
     const ScanArgs &a = p.a;
     const int HW = p.c.hw, BR = p.c.br, TPR = p.c.tpr, NS = p.c.nstages;
     const int tid = threadIdx.x;
     const int nthr_c = blockDim.x - 32;
     const int lane = tid & 31;
-    const bool has_x = (K == 3) && (a.skip_type == 1);
+    constexpr bool has_x = (K == 3);   // k = 3 without a highway term is served by the generic kernel
     const int64_t D = (int64_t)a.d * a.dirs;
     const int ht = blockIdx.x % p.c.nht, rt = blockIdx.x / p.c.nht;
     const int64_t dj0 = (int64_t)ht * HW;
@@ -95,37 +157,50 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const PipeArgs p) {
 
     if (tid >= nthr_c) {
         // ------------------------------ producer warp ------------------------------
-        const T *u = (const T *)a.u;
-        const T *x = (const T *)a.x;
+        const uint8_t *u = (const uint8_t *)a.u;
+        const uint8_t *x = (const uint8_t *)a.x;
         const int ntens = has_x ? 2 : 1;
+        const int nslots = kTS * nrows * ntens;
+        const int per_lane = (nslots + 31) / 32;
+        if (per_lane > kSlotsPerLane) { if (lane == 0) atomicExch(p.err, 5); return; }  // host never picks such a tile
+        const int64_t tstride = (dir ? -1 : 1) * a.B * D * (int64_t)sizeof(T);   // bytes per time step (x)
+        CopySlot slot[kSlotsPerLane];
+#pragma unroll
+        for (int j = 0; j < kSlotsPerLane; ++j) {
+            const int idx = lane + 32 * j;
+            const int which = idx % ntens;
+            const int rr = (idx / ntens) % nrows;
+            const int ts = idx / (ntens * nrows);
+            const int64_t t = dir ? (L - 1 - ts) : ts;
+            const int64_t o = ((t * a.B + b0 + rr) * D + dj0) * (int64_t)sizeof(T);
+            slot[j].ts = (idx < nslots) ? ts : kTS;
+            slot[j].is_cprev = 0;
+            if (which == 0) {
+                slot[j].src = u + o * K; slot[j].stage_step = tstride * K * kTS;
+                slot[j].dst_off = (ts * BR + rr) * u_slab; slot[j].bytes = u_slab;
+            } else {
+                slot[j].src = x + o; slot[j].stage_step = tstride * kTS;
+                slot[j].dst_off = u_region + (ts * BR + rr) * x_slab; slot[j].bytes = x_slab;
+            }
+        }
+        int s = 0;
+        uint32_t ph = 1;   // the first pass over the ring finds every stage free
         for (int it = 0; it < nst; ++it) {
-            const int s = it % NS;
-            if (it >= NS) {
-                if (!mbar_wait_bounded(bar_empty + 8 * s, ((it / NS) - 1) & 1)) {
-                    if (lane == 0) atomicExch(p.err, 1);
-                    break;
-                }
+            if (!mbar_wait_bounded(bar_empty + 8 * s, ph)) {
+                if (lane == 0) atomicExch(p.err, 1);
+                break;
             }
-            const int64_t n0 = (int64_t)it * kTS;
-            const int steps = (int)min((int64_t)kTS, L - n0);
-            if (lane == 0)
-                mbar_arrive_expect_tx(bar_full + 8 * s, (uint32_t)steps * nrows * (u_slab + x_slab));
+            const int steps = (int)min((int64_t)kTS, L - (int64_t)it * kTS);
+            const uint32_t bar = bar_full + 8 * s;
+            if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)steps * nrows * (u_slab + x_slab));
             __syncwarp();
-            const uint32_t sbase = smem_u32(stage0 + (size_t)s * stage_bytes);
-            const int ncopies = steps * nrows * ntens;
-            for (int idx = lane; idx < ncopies; idx += 32) {
-                const int which = idx % ntens;
-                const int rr = (idx / ntens) % nrows;
-                const int ts = idx / (ntens * nrows);
-                const int64_t n = n0 + ts;
-                const int64_t t = dir ? (L - 1 - n) : n;
-                const int64_t o = ((t * a.B + b0 + rr) * D + dj0);
-                if (which == 0)
-                    bulk_copy_g2s(sbase + (ts * BR + rr) * u_slab, u + o * K, u_slab, bar_full + 8 * s);
-                else
-                    bulk_copy_g2s(sbase + u_region + (ts * BR + rr) * x_slab, x + o, x_slab,
-                                  bar_full + 8 * s);
+            const uint32_t sbase = smem_u32(stage0) + (uint32_t)s * stage_bytes;
+#pragma unroll
+            for (int j = 0; j < kSlotsPerLane; ++j) {
+                if (slot[j].ts < steps) bulk_copy_g2s(sbase + slot[j].dst_off, slot[j].src, slot[j].bytes, bar);
+                slot[j].src += slot[j].stage_step;
             }
+            if (++s == NS) { s = 0; ph ^= 1; }
         }
         return;
     }
@@ -137,6 +212,7 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const PipeArgs p) {
     const int64_t b = b0 + (active ? r : 0);
     const int64_t col = b * D + dj0 + hc;
     const bool has_pad = a.mask_pad != nullptr;
+    const bool has_hist = a.c_hist != nullptr;
 
     float c[V], wc1n[V], wc2n[V], b1n[V], b2n[V], mk[V];
 #pragma unroll
@@ -161,7 +237,6 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const PipeArgs p) {
     const int64_t t_first = dir ? (L - 1) : 0;
     const int64_t ostep = dir ? -(a.B * D) : (a.B * D);
     T *hp = (T *)a.h + (t_first * a.B + b) * D + dj0 + hc;
-    const bool has_hist = a.c_hist != nullptr;
     TC *cp = (TC *)a.c_hist + (has_hist ? (t_first * a.B + b) * D + dj0 + hc : 0);
     const int64_t pstep = dir ? -a.B : a.B;
     const uint8_t *pp = has_pad ? a.mask_pad + t_first * a.B + b : nullptr;
@@ -180,62 +255,74 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const PipeArgs p) {
         }
         return bits;
     };
-    uint32_t pad0 = load_pad(0), pad1 = load_pad(kTS);
 
-    int s = 0;
-    uint32_t ph = 0;
-    for (int it = 0; it < nst; ++it) {
-        if (!mbar_wait_bounded(bar_full + 8 * s, ph)) {
-            atomicExch(p.err, 2);
-            break;
-        }
-        const uint32_t pad_cur = pad0;
-        pad0 = pad1;
-        pad1 = load_pad((int64_t)(it + 2) * kTS);
-        const uint8_t *sb = stage0 + (size_t)s * stage_bytes;
-        const int steps = (int)min((int64_t)kTS, L - (int64_t)it * kTS);
-        if (active) {
+    // One stage of kTS steps.  PAD / HIST / FULL are compile-time, so the unrolled body has no
+    // branch: padded steps keep c and emit 0 through selects.
+    auto stage = [&](const uint8_t *sb, uint32_t pad_bits, int steps, auto pad_c, auto hist_c, auto full_c) {
+        constexpr bool PAD = decltype(pad_c)::value, HIST = decltype(hist_c)::value, FULL = decltype(full_c)::value;
 #pragma unroll
-            for (int ts = 0; ts < kTS; ++ts) {
-                if (ts < steps) {
-                    Pack<T, V> ho;
-                    if (!((pad_cur >> ts) & 1u)) {
-                        const Pack<T, V * K> up = *reinterpret_cast<const Pack<T, V * K> *>(sb + u_off + ts * su);
-                        Pack<T, V> xp;
-                        if (has_x) xp = *reinterpret_cast<const Pack<T, V> *>(sb + x_off + ts * sx);
+        for (int ts = 0; ts < kTS; ++ts) {
+            if (!FULL && ts >= steps) break;
+            const bool pad = PAD && ((pad_bits >> ts) & 1u);
+            const Pack<T, V * K> up = *reinterpret_cast<const Pack<T, V * K> *>(sb + u_off + ts * su);
+            Pack<T, V> xp;
+            if (has_x) xp = *reinterpret_cast<const Pack<T, V> *>(sb + x_off + ts * sx);
+            float hv[V];
 #pragma unroll
-                        for (int i = 0; i < V; ++i) {
-                            const float u0 = Cvt<T>::to_f(up.v[i * K + 0]);
-                            const float u1 = Cvt<T>::to_f(up.v[i * K + 1]);
-                            const float u2 = Cvt<T>::to_f(up.v[i * K + 2]);
-                            float xv = 0.f;
-                            if (K == 4) xv = Cvt<T>::to_f(up.v[i * K + K - 1]);
-                            else if (has_x) xv = Cvt<T>::to_f(xp.v[i]) * scale;
-                            const float g1 = G::eval(c[i], wc1n[i], u1, b1n[i]);
-                            const float g2 = G::eval(c[i], wc2n[i], u2, b2n[i]);
-                            c[i] = fmaf(c[i] - u0, g1, u0);
-                            ho.v[i] = Cvt<T>::from_f(fmaf((c[i] - xv) * mk[i], g2, xv));
-                        }
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < V; ++i) ho.v[i] = Cvt<T>::from_f(0.f);
-                    }
-                    *reinterpret_cast<Pack<T, V> *>(hp) = ho;
-                    hp += ostep;
-                    if (has_hist) {
-                        Pack<TC, V> co;
-#pragma unroll
-                        for (int i = 0; i < V; ++i) co.v[i] = Cvt<TC>::from_f(c[i]);
-                        *reinterpret_cast<Pack<TC, V> *>(cp) = co;
-                        cp += ostep;
-                    }
-                }
+            for (int i = 0; i < V; ++i) {
+                const float u0 = Cvt<T>::to_f(up.v[i * K + 0]);
+                const float u1 = Cvt<T>::to_f(up.v[i * K + 1]);
+                const float u2 = Cvt<T>::to_f(up.v[i * K + 2]);
+                const float xv = (K == 4) ? Cvt<T>::to_f(up.v[i * K + K - 1]) : Cvt<T>::to_f(xp.v[i]) * scale;
+                const float g1 = G::eval(c[i], wc1n[i], u1, b1n[i]);
+                const float g2 = G::eval(c[i], wc2n[i], u2, b2n[i]);
+                const float cn = fmaf(c[i] - u0, g1, u0);
+                const float hn = fmaf((cn - xv) * mk[i], g2, xv);
+                c[i] = pad ? c[i] : cn;
+                hv[i] = pad ? 0.f : hn;
+            }
+            Pack<T, V> ho;
+            pack_from_float(ho, hv);
+            *reinterpret_cast<Pack<T, V> *>(hp) = ho;
+            hp += ostep;
+            if (HIST) {
+                Pack<TC, V> co;
+                pack_from_float(co, c);
+                *reinterpret_cast<Pack<TC, V> *>(cp) = co;
+                cp += ostep;
             }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_empty + 8 * s);
-        if (++s == NS) { s = 0; ph ^= 1; }
+    };
+
+    auto run = [&](auto pad_c, auto hist_c) {
+        uint32_t pad0 = load_pad(0), pad1 = load_pad(kTS);
+        int s = 0;
+        uint32_t ph = 0;
+        for (int it = 0; it < nst; ++it) {
+            if (!mbar_wait_bounded(bar_full + 8 * s, ph)) {
+                atomicExch(p.err, 2);
+                break;
+            }
+            const uint32_t pad_cur = pad0;
+            pad0 = pad1;
+            pad1 = load_pad((int64_t)(it + 2) * kTS);
+            const uint8_t *sb = stage0 + (size_t)s * stage_bytes;
+            const int64_t left = L - (int64_t)it * kTS;
+            if (active) {
+                if (left >= kTS) stage(sb, pad_cur, kTS, pad_c, hist_c, BoolC<true>{});
+                else stage(sb, pad_cur, (int)left, pad_c, hist_c, BoolC<false>{});
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty + 8 * s);
+            if (++s == NS) { s = 0; ph ^= 1; }
+        }
+    };
+    if (has_pad) {
+        if (has_hist) run(BoolC<true>{}, BoolC<true>{}); else run(BoolC<true>{}, BoolC<false>{});
+    } else {
+        if (has_hist) run(BoolC<false>{}, BoolC<true>{}); else run(BoolC<false>{}, BoolC<false>{});
     }
+
     if (a.c_last && active) {
         Pack<float, V> cl;
 #pragma unroll
@@ -252,13 +339,13 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const PipeArgs p) {
 template <typename T, typename TC, int V, int K>
 __global__ void __launch_bounds__(160) scan_bwd_pipe(const PipeArgs p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    using G = Gate<sizeof(T) == 4>;
+    using G = GateFor<T>;
     const ScanArgs &a = p.a;
     const int HW = p.c.hw, BR = p.c.br, TPR = p.c.tpr, NS = p.c.nstages;
     const int tid = threadIdx.x;
     const int nthr_c = blockDim.x - 32;
     const int lane = tid & 31;
-    const bool has_x = (K == 3) && (a.skip_type == 1);
+    constexpr bool has_x = (K == 3);
     const int64_t D = (int64_t)a.d * a.dirs;
     const int ht = blockIdx.x % p.c.nht, rt = blockIdx.x / p.c.nht;
     const int64_t dj0 = (int64_t)ht * HW;
@@ -298,55 +385,72 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const PipeArgs p) {
 
     if (tid >= nthr_c) {
         // ------------------------------ producer warp ------------------------------
-        const T *u = (const T *)a.u;
-        const T *x = (const T *)a.x;
-        const TC *chp = (const TC *)a.c_hist;
-        const T *gh = (const T *)a.grad_h;
+        const uint8_t *u = (const uint8_t *)a.u;
+        const uint8_t *x = (const uint8_t *)a.x;
+        const uint8_t *chp = (const uint8_t *)a.c_hist;
+        const uint8_t *gh = (const uint8_t *)a.grad_h;
         const int ntens = has_x ? 4 : 3;
-        for (int it = 0; it < nst; ++it) {
-            const int s = it % NS;
-            if (it >= NS) {
-                if (!mbar_wait_bounded(bar_empty + 8 * s, ((it / NS) - 1) & 1)) {
-                    if (lane == 0) atomicExch(p.err, 3);
-                    break;
-                }
+        const int nslots = kTS * nrows * ntens;
+        const int per_lane = (nslots + 31) / 32;
+        bool ok = per_lane <= kSlotsPerLane;
+        if (!ok && lane == 0) atomicExch(p.err, 6);   // host never picks such a tile
+        // backward step m visits time t = dir ? m : L-1-m; its predecessor state sits one step earlier
+        // in the forward's scan order, i.e. at t + (dir ? 1 : -1)
+        const int64_t tsign = dir ? 1 : -1;
+        const int64_t row_t = a.B * D * (int64_t)sizeof(T);    // bytes per time step, T tensors
+        const int64_t row_c = a.B * D * (int64_t)sizeof(TC);
+        CopySlot slot[kSlotsPerLane];
+#pragma unroll
+        for (int j = 0; j < kSlotsPerLane; ++j) {
+            const int idx = lane + 32 * j;
+            const int which = idx % ntens;
+            const int rr = (idx / ntens) % nrows;
+            const int ts = idx / (ntens * nrows);
+            const int64_t t = dir ? ts : (L - 1 - ts);
+            const int64_t e = (t * a.B + b0 + rr) * D + dj0;   // element offset of the row slab
+            slot[j].ts = (ok && idx < nslots) ? ts : kTS;
+            slot[j].is_cprev = 0;
+            if (which == 0) {
+                slot[j].src = u + e * K * (int64_t)sizeof(T); slot[j].stage_step = tsign * row_t * K * kTS;
+                slot[j].dst_off = (ts * BR + rr) * u_slab; slot[j].bytes = u_slab;
+            } else if (which == 1) {
+                slot[j].src = gh + e * (int64_t)sizeof(T); slot[j].stage_step = tsign * row_t * kTS;
+                slot[j].dst_off = u_region + x_region + c_region + (ts * BR + rr) * g_slab; slot[j].bytes = g_slab;
+            } else if (which == 2) {
+                // c at the forward's previous scan step: one time step further along the backward walk
+                slot[j].src = chp + e * (int64_t)sizeof(TC) + tsign * row_c; slot[j].stage_step = tsign * row_c * kTS;
+                slot[j].dst_off = u_region + x_region + (ts * BR + rr) * c_slab; slot[j].bytes = c_slab;
+                slot[j].is_cprev = 1;
+            } else {
+                slot[j].src = x + e * (int64_t)sizeof(T); slot[j].stage_step = tsign * row_t * kTS;
+                slot[j].dst_off = u_region + (ts * BR + rr) * x_slab; slot[j].bytes = x_slab;
             }
-            const int64_t m0 = (int64_t)it * kTS;
-            const int steps = (int)min((int64_t)kTS, L - m0);
-            // the step with n == 0 (m == L-1) has no c[t-1] slab: c_init is used instead
-            const bool has_first = (m0 + steps == L);
+        }
+        int s = 0;
+        uint32_t ph = 1;
+        for (int it = 0; it < nst && ok; ++it) {
+            if (!mbar_wait_bounded(bar_empty + 8 * s, ph)) {
+                if (lane == 0) atomicExch(p.err, 3);
+                break;
+            }
+            const int64_t left = L - (int64_t)it * kTS;
+            const int steps = (int)min((int64_t)kTS, left);
+            const int last_ts = (left <= kTS) ? (int)left - 1 : kTS;   // the step that starts from c_init
+            const uint32_t bar = bar_full + 8 * s;
             if (lane == 0) {
                 uint32_t bytes = (uint32_t)steps * nrows * (u_slab + x_slab + c_slab + g_slab);
-                if (has_first) bytes -= (uint32_t)nrows * c_slab;
-                mbar_arrive_expect_tx(bar_full + 8 * s, bytes);
+                if (left <= kTS) bytes -= (uint32_t)nrows * c_slab;
+                mbar_arrive_expect_tx(bar, bytes);
             }
             __syncwarp();
-            const uint32_t sbase = smem_u32(stage0 + (size_t)s * stage_bytes);
-            const int ncopies = steps * nrows * ntens;
-            for (int idx = lane; idx < ncopies; idx += 32) {
-                const int which = idx % ntens;
-                const int rr = (idx / ntens) % nrows;
-                const int ts = idx / (ntens * nrows);
-                const int64_t n = L - 1 - (m0 + ts);
-                const int64_t t = dir ? (L - 1 - n) : n;
-                const int64_t o = ((t * a.B + b0 + rr) * D + dj0);
-                const uint32_t bar = bar_full + 8 * s;
-                if (which == 0) {
-                    bulk_copy_g2s(sbase + (ts * BR + rr) * u_slab, u + o * K, u_slab, bar);
-                } else if (which == 1) {
-                    bulk_copy_g2s(sbase + u_region + x_region + c_region + (ts * BR + rr) * g_slab,
-                                  gh + o, g_slab, bar);
-                } else if (which == 2) {
-                    if (n > 0) {
-                        const int64_t tp = dir ? (t + 1) : (t - 1);
-                        const int64_t op = ((tp * a.B + b0 + rr) * D + dj0);
-                        bulk_copy_g2s(sbase + u_region + x_region + (ts * BR + rr) * c_slab, chp + op,
-                                      c_slab, bar);
-                    }
-                } else {
-                    bulk_copy_g2s(sbase + u_region + (ts * BR + rr) * x_slab, x + o, x_slab, bar);
-                }
+            const uint32_t sbase = smem_u32(stage0) + (uint32_t)s * stage_bytes;
+#pragma unroll
+            for (int j = 0; j < kSlotsPerLane; ++j) {
+                if (slot[j].ts < steps && !(slot[j].is_cprev && slot[j].ts == last_ts))
+                    bulk_copy_g2s(sbase + slot[j].dst_off, slot[j].src, slot[j].bytes, bar);
+                slot[j].src += slot[j].stage_step;
             }
+            if (++s == NS) { s = 0; ph ^= 1; }
         }
     } else {
         // -------------------------------- consumers --------------------------------
@@ -397,84 +501,93 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const PipeArgs p) {
             }
             return bits;
         };
-        uint32_t pad0 = load_pad(0), pad1 = load_pad(kTS);
 
-        int s = 0;
-        uint32_t ph = 0;
-        for (int it = 0; it < nst; ++it) {
-            if (!mbar_wait_bounded(bar_full + 8 * s, ph)) {
-                atomicExch(p.err, 4);
-                break;
-            }
-            const uint32_t pad_cur = pad0;
-            pad0 = pad1;
-            pad1 = load_pad((int64_t)(it + 2) * kTS);
-            const uint8_t *sb = stage0 + (size_t)s * stage_bytes;
-            const int64_t left = L - (int64_t)it * kTS;   // steps left including this stage
-            const int steps = (int)min((int64_t)kTS, left);
-            if (active) {
+        // One stage.  LAST marks the final stage (ragged, and holding the step whose predecessor
+        // state is c_init); all other stages are full and branch-free.
+        auto stage = [&](const uint8_t *sb, uint32_t pad_bits, int steps, auto pad_c, auto last_c) {
+            constexpr bool PAD = decltype(pad_c)::value, LAST = decltype(last_c)::value;
 #pragma unroll
-                for (int ts = 0; ts < kTS; ++ts) {
-                    if (ts < steps) {
-                        Pack<T, V * K> guo;
-                        Pack<T, V> gxo;
-                        if (!((pad_cur >> ts) & 1u)) {
-                            const bool at_start = (ts == left - 1);   // n == 0: the state before it is c_init
-                            const Pack<T, V * K> up = *reinterpret_cast<const Pack<T, V * K> *>(sb + u_off + ts * su);
-                            const Pack<T, V> ghp = *reinterpret_cast<const Pack<T, V> *>(sb + g_off + ts * sg);
-                            Pack<T, V> xp;
-                            if (has_x) xp = *reinterpret_cast<const Pack<T, V> *>(sb + x_off + ts * sx);
-                            Pack<TC, V> cpp;
-                            if (!at_start) cpp = *reinterpret_cast<const Pack<TC, V> *>(sb + c_off + ts * sc);
+            for (int ts = 0; ts < kTS; ++ts) {
+                if (LAST && ts >= steps) break;
+                const bool pad = PAD && ((pad_bits >> ts) & 1u);
+                const bool at_start = LAST && (ts == steps - 1);
+                const Pack<T, V * K> up = *reinterpret_cast<const Pack<T, V * K> *>(sb + u_off + ts * su);
+                const Pack<T, V> ghp = *reinterpret_cast<const Pack<T, V> *>(sb + g_off + ts * sg);
+                Pack<T, V> xp;
+                if (has_x) xp = *reinterpret_cast<const Pack<T, V> *>(sb + x_off + ts * sx);
+                const Pack<TC, V> cpp = *reinterpret_cast<const Pack<TC, V> *>(sb + c_off + ts * sc);
+                float guv[V * K], gxv_[V];
 #pragma unroll
-                            for (int i = 0; i < V; ++i) {
-                                const float u0 = Cvt<T>::to_f(up.v[i * K + 0]);
-                                const float u1 = Cvt<T>::to_f(up.v[i * K + 1]);
-                                const float u2 = Cvt<T>::to_f(up.v[i * K + 2]);
-                                float xv = 0.f;
-                                if (K == 4) xv = Cvt<T>::to_f(up.v[i * K + K - 1]);
-                                else if (has_x) xv = Cvt<T>::to_f(xp.v[i]) * scale;
-                                const float cp = at_start ? c0[i] : Cvt<TC>::to_f(cpp.v[i]);
-                                const float gh = Cvt<T>::to_f(ghp.v[i]);
-                                const float g1 = G::eval(cp, wc1n[i], u1, b1n[i]);
-                                const float g2 = G::eval(cp, wc2n[i], u2, b2n[i]);
-                                const float dc = cp - u0;
-                                const float cv = fmaf(dc, g1, u0);
-                                const float ghm = gh * mk[i];
-                                const float gg2 = ghm * (cv - xv) * (g2 - g2 * g2);
-                                const float gc = fmaf(ghm, g2, cur[i]);
-                                const float gg1 = gc * dc * (g1 - g1 * g1);
-                                gb1[i] += gg1;
-                                gb2[i] += gg2;
-                                gwc1[i] = fmaf(gg1, cp, gwc1[i]);
-                                gwc2[i] = fmaf(gg2, cp, gwc2[i]);
-                                cur[i] = fmaf(gc, g1, G::kUnfold * fmaf(gg1, wc1n[i], gg2 * wc2n[i]));
-                                const float gxv = fmaf(-ghm, g2, gh);
-                                guo.v[i * K + 0] = Cvt<T>::from_f(fmaf(-gc, g1, gc));
-                                guo.v[i * K + 1] = Cvt<T>::from_f(gg1);
-                                guo.v[i * K + 2] = Cvt<T>::from_f(gg2);
-                                if (K == 4) guo.v[i * K + K - 1] = Cvt<T>::from_f(gxv);
-                                gxo.v[i] = Cvt<T>::from_f(gxv * scale);
-                            }
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < V * K; ++i) guo.v[i] = Cvt<T>::from_f(0.f);
-#pragma unroll
-                            for (int i = 0; i < V; ++i) gxo.v[i] = Cvt<T>::from_f(0.f);
-                        }
-                        *reinterpret_cast<Pack<T, V * K> *>(gup) = guo;
-                        gup += ostep * K;
-                        if (has_x) {
-                            *reinterpret_cast<Pack<T, V> *>(gxp) = gxo;
-                            gxp += ostep;
-                        }
+                for (int i = 0; i < V; ++i) {
+                    const float u0 = Cvt<T>::to_f(up.v[i * K + 0]);
+                    const float u1 = Cvt<T>::to_f(up.v[i * K + 1]);
+                    const float u2 = Cvt<T>::to_f(up.v[i * K + 2]);
+                    const float xv = (K == 4) ? Cvt<T>::to_f(up.v[i * K + K - 1]) : Cvt<T>::to_f(xp.v[i]) * scale;
+                    const float cprev = at_start ? c0[i] : Cvt<TC>::to_f(cpp.v[i]);
+                    const float gh = Cvt<T>::to_f(ghp.v[i]);
+                    const float g1 = G::eval(cprev, wc1n[i], u1, b1n[i]);
+                    const float g2 = G::eval(cprev, wc2n[i], u2, b2n[i]);
+                    const float dc = cprev - u0;
+                    const float cv = fmaf(dc, g1, u0);
+                    const float ghm = gh * mk[i];
+                    float gg2 = ghm * (cv - xv) * (g2 - g2 * g2);
+                    const float gc = fmaf(ghm, g2, cur[i]);
+                    float gg1 = gc * dc * (g1 - g1 * g1);
+                    float gu0 = fmaf(-gc, g1, gc);
+                    float gxv = fmaf(-ghm, g2, gh);
+                    const float curn = fmaf(gc, g1, G::kUnfold * fmaf(gg1, wc1n[i], gg2 * wc2n[i]));
+                    if (PAD) {
+                        gg1 = pad ? 0.f : gg1; gg2 = pad ? 0.f : gg2; gu0 = pad ? 0.f : gu0; gxv = pad ? 0.f : gxv;
                     }
+                    cur[i] = pad ? cur[i] : curn;
+                    gb1[i] += gg1;
+                    gb2[i] += gg2;
+                    gwc1[i] = fmaf(gg1, cprev, gwc1[i]);
+                    gwc2[i] = fmaf(gg2, cprev, gwc2[i]);
+                    guv[i * K + 0] = gu0;
+                    guv[i * K + 1] = gg1;
+                    guv[i * K + 2] = gg2;
+                    if (K == 4) guv[i * K + K - 1] = gxv;
+                    gxv_[i] = gxv * scale;
+                }
+                Pack<T, V * K> guo;
+                pack_from_float(guo, guv);
+                *reinterpret_cast<Pack<T, V * K> *>(gup) = guo;
+                gup += ostep * K;
+                if (has_x) {
+                    Pack<T, V> gxo;
+                    pack_from_float(gxo, gxv_);
+                    *reinterpret_cast<Pack<T, V> *>(gxp) = gxo;
+                    gxp += ostep;
                 }
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_empty + 8 * s);
-            if (++s == NS) { s = 0; ph ^= 1; }
-        }
+        };
+
+        auto run = [&](auto pad_c) {
+            uint32_t pad0 = load_pad(0), pad1 = load_pad(kTS);
+            int s = 0;
+            uint32_t ph = 0;
+            for (int it = 0; it < nst; ++it) {
+                if (!mbar_wait_bounded(bar_full + 8 * s, ph)) {
+                    atomicExch(p.err, 4);
+                    break;
+                }
+                const uint32_t pad_cur = pad0;
+                pad0 = pad1;
+                pad1 = load_pad((int64_t)(it + 2) * kTS);
+                const uint8_t *sb = stage0 + (size_t)s * stage_bytes;
+                const int64_t left = L - (int64_t)it * kTS;   // steps left including this stage
+                if (active) {
+                    if (left > kTS) stage(sb, pad_cur, kTS, pad_c, BoolC<false>{});
+                    else stage(sb, pad_cur, (int)left, pad_c, BoolC<true>{});
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_empty + 8 * s);
+                if (++s == NS) { s = 0; ph ^= 1; }
+            }
+        };
+        if (has_pad) run(BoolC<true>{}); else run(BoolC<false>{});
+
         if (active) {
             Pack<float, V> gi;
 #pragma unroll
@@ -536,11 +649,11 @@ static bool choose_tile(int64_t L, int64_t B, int64_t d, int dirs, int k, int sk
     if (d % granule != 0 || L < 1 || B < 1) return false;
     const int64_t D = d * dirs, ncols = B * D;
     const int sms = num_sms();
-    const int vmax = granule, vmin = (s == 2) ? 2 : 1;
-    // Columns per thread.  Measured on B200: with three or more warps per SM available, V = 4
-    // amortises the per-step overhead best (V = 8 costs registers and occupancy for nothing);
-    // smaller problems are bound by per-step latency and want as many warps as possible.
-    int v = (ncols / (32 * 4) >= (int64_t)sms * 3 && vmax >= 4) ? 4 : vmin;
+    const int vmax = 4, vmin = 2;
+    // Columns per thread, from sweeps on B200: V = 4 amortises the per-step overhead best once it
+    // still leaves eight or more warps per SM; below that the scan is bound by per-step latency
+    // and V = 2 (twice the warps) wins.  V = 1 and V = 8 never did.
+    int v = (ncols / (32 * 4) >= (int64_t)sms * 8) ? 4 : 2;
     v = env_int(backward ? "SRU_B200_BWD_V" : "SRU_B200_FWD_V", v);
     if (v < vmin || v > vmax || (v & (v - 1))) return false;
     // consumer threads per CTA: two warps, one when that is needed to give every SM a CTA
@@ -555,6 +668,8 @@ static bool choose_tile(int64_t L, int64_t B, int64_t d, int dirs, int k, int sk
     if (hw == 0) return false;
     const int tpr = hw / v;
     int br = (int)std::min<int64_t>(B, std::max(1, ntc / tpr));
+    // the producer warp keeps at most kSlotsPerLane copies per lane and stage: kTS * br * tensors <= 128
+    br = std::min(br, (32 * kSlotsPerLane) / (kTS * (backward ? 4 : 2)));
     const int cthreads = ((br * tpr + 31) / 32) * 32;
     if (cthreads > 128) return false;
     const bool has_x = (k == 3 && skip_type == 1);
@@ -585,7 +700,7 @@ static bool choose_tile(int64_t L, int64_t B, int64_t d, int dirs, int k, int sk
 
 static bool pipelined_eligible(const ScanArgs &a) {
     if (a.is_custom || a.activation_type != 0) return false;
-    if (a.k == 3 && a.skip_type == 2) return false;
+    if (a.k == 3 && a.skip_type != 1) return false;   // k = 3 without a highway term: generic kernel
     if (a.k == 4 && a.skip_type != 2) return false;
     if (a.dtype == SRU_F64) return false;
     if (env_int("SRU_B200_FORCE_GENERIC", 0)) return false;
@@ -615,12 +730,9 @@ static int launch_t(const PipeArgs &p, bool backward, cudaStream_t st) {
 
 template <typename T, typename TC, int K>
 static int launch_v(const PipeArgs &p, bool backward, cudaStream_t st) {
-    constexpr int s = sizeof(T);
     switch (p.c.v) {
-        case 1: if constexpr (s == 4) return launch_t<T, TC, 1, K>(p, backward, st); break;
         case 2: return launch_t<T, TC, 2, K>(p, backward, st);
         case 4: return launch_t<T, TC, 4, K>(p, backward, st);
-        case 8: if constexpr (s == 2) return launch_t<T, TC, 8, K>(p, backward, st); break;
     }
     return set_error(SRU_ERR_UNSUPPORTED, "columns per thread %d", p.c.v);
 }

@@ -71,10 +71,6 @@ class _Projection(Function):
         # x (M, K), w (K, N), both already in the 16-bit compute dtype
         ctx.save_for_backward(x, w)
         ctx.has_bias = col_bias is not None
-        if x.size(0) >= 4 * w.size(0):
-            # Many more rows than weights: a K-major copy of W (a few MB, made once per call)
-            # lets both operands stream as K-major tiles, the fastest operand form of the kernel.
-            return gemm(x, w.t().contiguous(), trans_b=True, col_bias=col_bias, name="gemm_fwd")
         return gemm(x, w, col_bias=col_bias)
 
     @staticmethod
