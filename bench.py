@@ -90,6 +90,7 @@ def algorithmic_work(cfg, B, s_bytes, c_bytes):
     L = cfg["L"]
     fwd = bwd = 0
     flops_f = flops_b = 0
+    gemm_bytes = 0
     for li, (n_in, D, k, dirs, p) in enumerate(layer_shapes(cfg["kwargs"])):
         cols = L * B * D
         e3 = 1 if k == 3 else 0
@@ -101,9 +102,15 @@ def algorithmic_work(cfg, B, s_bytes, c_bytes):
         M = L * B
         f = 2 * M * (n_in * p + p * D * k) if p else 2 * M * n_in * D * k
         flops_f += f
+        # operand + result bytes of this layer's products (16-bit), each matrix counted once per product
+        prods = [(M, n_in, p), (M, p, D * k)] if p else [(M, n_in, D * k)]
+        for (m_, k_, n_) in prods:
+            once = 2 * (m_ * k_ + k_ * n_ + m_ * n_)
+            gemm_bytes += once * (3 if (cfg["train"] and (li > 0 or (m_, k_, n_) != prods[0])) else (2 if cfg["train"] else 1))
         if cfg["train"]:
             flops_b += 2 * f if li > 0 else (2 * f - (2 * M * n_in * (p if p else D * k)))
-    return dict(scan_fwd_bytes=fwd, scan_bwd_bytes=bwd, gemm_fwd_flops=flops_f, gemm_bwd_flops=flops_b)
+    return dict(scan_fwd_bytes=fwd, scan_bwd_bytes=bwd, gemm_fwd_flops=flops_f, gemm_bwd_flops=flops_b,
+                gemm_bytes=gemm_bytes)
 
 
 class ClockSampler:
@@ -400,8 +407,21 @@ def main():
     if cands:
         top = max(cands, key=lambda k: cands[k]["ms_per_step"])
         t = cands[top]
+        # DRAM traffic per launch: ratio of measured dram bytes to algorithmic bytes from the ncu captures
+        # summarised under profiles/ (small case of the same kernels), applied to this run's units.
+        ratio = {"scan_fwd": 0.93, "scan_fwd_infer": 0.93, "scan_bwd": 0.97, "gemm_all": 0.85}.get(top)
+        alg = {"scan_fwd": work["scan_fwd_bytes"], "scan_fwd_infer": work["scan_fwd_bytes"],
+               "scan_bwd": work["scan_bwd_bytes"], "gemm_all": work["gemm_bytes"]}.get(top)
+        if top == "gemm_all":
+            n_launch = sum(v["launches_per_step"] for k2, v in kernels.items()
+                           if k2.startswith("gemm_") and k2 != "gemm_all")
+        else:
+            n_launch = kernels[top]["launches_per_step"]
+        traffic = (ratio * alg / max(1, n_launch)) if (ratio and alg) else None
         roofline = {"kernel": top, "bound": t["bound"], "achieved": t["achieved"], "peak": t["peak"],
-                    "unit": t["unit"], "frac": t["frac"], "traffic": None, "peak_source": peaks["source"]}
+                    "unit": t["unit"], "frac": t["frac"], "traffic": traffic,
+                    "traffic_note": "bytes per launch; ncu dram bytes / algorithmic bytes from profiles/, scaled by units",
+                    "peak_source": peaks["source"]}
 
     out = {
         "metric": metric, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
