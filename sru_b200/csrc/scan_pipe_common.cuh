@@ -1,0 +1,98 @@
+// Pieces shared by the pipelined scan kernels: pipeline constants, the kernel argument block,
+// gate evaluation, packed conversions and the producer's copy-slot bookkeeping.
+#pragma once
+#include <cuda.h>
+
+#include <type_traits>
+
+#include "scan.cuh"
+
+namespace srub {
+
+constexpr int kTS = 4;            // time steps per pipeline stage
+constexpr int kBarBytes = 256;    // room for 2 * 16 mbarriers at the start of shared memory
+constexpr int kMaxStages = 16;
+
+struct PipeArgs {
+    ScanArgs a;
+    TileCfg c;
+    int *err;
+};
+
+__device__ __forceinline__ float tanh_approx(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Gate evaluation s(u + wc*c + b).
+//  MODE 0 (fp32 storage): the reference's own expression 1/(1+expf(-z)) with full-precision
+//         expf and IEEE division, so fp32 results stay within 1e-5 of an fp32 CPU run.
+//  MODE 1: -log2(e) folded into wc and b once per column, ex2.approx + rcp.approx.
+//  MODE 2 (16-bit storage): s(z) = 0.5*tanh(z/2) + 0.5 with 1/2 folded into wc and b and one
+//         tanh.approx per gate: half the special-function work and the shortest serial chain
+//         (fma -> tanh -> fma).  Its absolute error (about 3e-4) is below bf16 / fp16 output
+//         rounding and inside the 2e-2 bar of the 16-bit modes.
+template <int MODE> struct Gate {
+    static __device__ __forceinline__ float fold(float v) {
+        return MODE == 0 ? v : (MODE == 1 ? v * kNegLog2e : v * 0.5f);
+    }
+    // multiplies (gg1*wc1f + gg2*wc2f) back to (gg1*wc1 + gg2*wc2)
+    static constexpr float kUnfold = MODE == 0 ? 1.f : (MODE == 1 ? -0.6931471805599453f : 2.f);
+    static __device__ __forceinline__ float eval(float c, float wcf, float u, float bf) {
+        if (MODE == 0) {
+            const float z = fmaf(wcf, c, u) + bf;
+            return 1.f / (1.f + expf(-z));
+        } else if (MODE == 1) {
+            return rcp_approx(1.f + ex2_approx(fmaf(c, wcf, fmaf(u, kNegLog2e, bf))));
+        } else {
+            return fmaf(tanh_approx(fmaf(c, wcf, fmaf(u, 0.5f, bf))), 0.5f, 0.5f);
+        }
+    }
+};
+template <typename T> using GateFor = Gate<sizeof(T) == 4 ? 0 : 2>;
+
+// float[N] -> Pack<T,N>, two values per conversion instruction for the 16-bit types.
+template <typename T, int N> __device__ __forceinline__ void pack_from_float(Pack<T, N> &out, const float (&v)[N]) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) out.v[i] = Cvt<T>::from_f(v[i]);
+}
+template <int N> __device__ __forceinline__ void pack_from_float(Pack<__nv_bfloat16, N> &out, const float (&v)[N]) {
+    if constexpr (N % 2 == 0) {
+#pragma unroll
+        for (int i = 0; i < N; i += 2)
+            *reinterpret_cast<__nv_bfloat162 *>(&out.v[i]) = __floats2bfloat162_rn(v[i], v[i + 1]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) out.v[i] = __float2bfloat16_rn(v[i]);
+    }
+}
+template <int N> __device__ __forceinline__ void pack_from_float(Pack<__half, N> &out, const float (&v)[N]) {
+    if constexpr (N % 2 == 0) {
+#pragma unroll
+        for (int i = 0; i < N; i += 2) *reinterpret_cast<__half2 *>(&out.v[i]) = __floats2half2_rn(v[i], v[i + 1]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) out.v[i] = __float2half_rn(v[i]);
+    }
+}
+
+// Tensor maps of the streamed tensors (3-D: row bytes / 8, batch, time), built on the host per launch.
+struct ScanMaps {
+    CUtensorMap u, x, c, g;   // U (and grad-independent inputs): x, saved states c, grad_h
+};
+
+// One TMA request: a box of (inner bytes/8) x rows x time steps into this CTA's shared memory.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
+__host__ __device__ __forceinline__ uint32_t align128(uint32_t v) { return (v + 127u) & ~127u; }
+
+template <bool B> using BoolC = std::integral_constant<bool, B>;
+
+
+}  // namespace srub

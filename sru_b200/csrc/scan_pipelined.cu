@@ -5,23 +5,25 @@
 // state (c, or dL/dc and the four parameter-gradient accumulators) in registers for the
 // whole sequence.  Time is the only sequential axis.
 //
-// Memory pipeline.  The per-step inputs of the tile (the gate pre-activations U, the
-// highway input x, and for backward c[t-1] and grad_h) are contiguous slabs of HW*k (or
-// HW) elements per row.  One extra warp, the producer, streams them kTS time steps at a
-// time into a ring of NS shared-memory stages with untiled bulk asynchronous copies
-// (cp.async.bulk, completion counted on an mbarrier per stage); consumers wait on the
-// stage's "full" barrier, read their 2..48-byte slices with vector shared loads, and
-// release the stage through its "empty" barrier.  The depth in time of the ring, not the
-// number of resident threads, provides the bytes in flight that HBM needs.  Outputs go
-// straight from registers to global memory with V*sizeof(T)-byte stores that are
-// contiguous across the warp.
+// Memory pipeline.  Every streamed tensor (the gate pre-activations U, the highway input x,
+// and for backward c[t-1] and grad_h) is described to the TMA engine by a 3-D tensor map
+// (row bytes, batch, time).  One elected producer thread per CTA issues ONE
+// cp.async.bulk.tensor request per tensor and ring stage: a box of SS time steps x BR rows x
+// the tile's hidden slice, landing in one of NS shared-memory stages and completing on that
+// stage's "full" mbarrier.  (Per-row untiled bulk copies were measured first: each costs the
+// issuing warp ~100 cycles, which capped small tiles at ~1 TB/s; a box request moves 4-16x
+// the bytes per instruction.)  Consumers wait on the stage's "full" barrier, read their
+// 4..48-byte slices with vector shared loads, and release the stage through its "empty"
+// barrier.  The depth in time of the ring, not the number of resident threads, provides the
+// bytes in flight that HBM needs.  Boxes that stick out of the tensor in time or batch are
+// zero-filled by the hardware.  Outputs go straight from registers to global memory with
+// V*sizeof(T)-byte stores that are contiguous across the warp.
 //
 // Latency.  Small problems leave about one warp per SM sub-partition, so what bounds them is
-// the dependent-instruction latency of one time step.  The body of a stage is therefore
+// the dependent-instruction latency of one time step.  The body of a 4-step block is therefore
 // branch-free (padding and the c_init boundary are selects, the options are template
-// parameters) and unrolled over the kTS steps of the stage, which lets the scheduler overlap
-// the loads, conversions and output arithmetic of neighbouring steps with the one chain that
-// is truly serial: c' -> gate -> c.
+// parameters) and unrolled, which lets the scheduler overlap the loads, conversions and output
+// arithmetic of neighbouring steps with the one chain that is truly serial: c' -> gate -> c.
 //
 // Every wait is bounded (mbar_wait_bounded); on a timeout the thread raises the device
 // error flag, stops processing and falls through to the end of the kernel.
@@ -30,101 +32,22 @@
 // :130-176 backward, with the direction taken from the tile instead of col % 2d):
 //   g1 = s(u1 + wc1*c' + b1), g2 = s(u2 + wc2*c' + b2), c = (c' - u0)*g1 + u0,
 //   h = (c - x')*m*g2 + x',  x' = x*scale_x (k=3) | u3 (k=4).
-#include <type_traits>
+#include <cudaTypedefs.h>
 
-#include "scan.cuh"
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+
+#include "scan_pipe_common.cuh"
 
 namespace srub {
 
-constexpr int kTS = 4;            // time steps per pipeline stage
-constexpr int kBarBytes = 256;    // room for 2 * 16 mbarriers at the start of shared memory
-constexpr int kMaxStages = 16;
-
-struct PipeArgs {
-    ScanArgs a;
-    TileCfg c;
-    int *err;
-};
-
-__device__ __forceinline__ float tanh_approx(float x) {
-    float y;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-
-// Gate evaluation s(u + wc*c + b).
-//  MODE 0 (fp32 storage): the reference's own expression 1/(1+expf(-z)) with full-precision
-//         expf and IEEE division, so fp32 results stay within 1e-5 of an fp32 CPU run.
-//  MODE 1: -log2(e) folded into wc and b once per column, ex2.approx + rcp.approx.
-//  MODE 2 (16-bit storage): s(z) = 0.5*tanh(z/2) + 0.5 with 1/2 folded into wc and b and one
-//         tanh.approx per gate: half the special-function work and the shortest serial chain
-//         (fma -> tanh -> fma).  Its absolute error (about 3e-4) is below bf16 / fp16 output
-//         rounding and inside the 2e-2 bar of the 16-bit modes.
-template <int MODE> struct Gate {
-    static __device__ __forceinline__ float fold(float v) {
-        return MODE == 0 ? v : (MODE == 1 ? v * kNegLog2e : v * 0.5f);
-    }
-    // multiplies (gg1*wc1f + gg2*wc2f) back to (gg1*wc1 + gg2*wc2)
-    static constexpr float kUnfold = MODE == 0 ? 1.f : (MODE == 1 ? -0.6931471805599453f : 2.f);
-    static __device__ __forceinline__ float eval(float c, float wcf, float u, float bf) {
-        if (MODE == 0) {
-            const float z = fmaf(wcf, c, u) + bf;
-            return 1.f / (1.f + expf(-z));
-        } else if (MODE == 1) {
-            return rcp_approx(1.f + ex2_approx(fmaf(c, wcf, fmaf(u, kNegLog2e, bf))));
-        } else {
-            return fmaf(tanh_approx(fmaf(c, wcf, fmaf(u, 0.5f, bf))), 0.5f, 0.5f);
-        }
-    }
-};
-template <typename T> using GateFor = Gate<sizeof(T) == 4 ? 0 : 2>;
-
-// float[N] -> Pack<T,N>, two values per conversion instruction for the 16-bit types.
-template <typename T, int N> __device__ __forceinline__ void pack_from_float(Pack<T, N> &out, const float (&v)[N]) {
-#pragma unroll
-    for (int i = 0; i < N; ++i) out.v[i] = Cvt<T>::from_f(v[i]);
-}
-template <int N> __device__ __forceinline__ void pack_from_float(Pack<__nv_bfloat16, N> &out, const float (&v)[N]) {
-    if constexpr (N % 2 == 0) {
-#pragma unroll
-        for (int i = 0; i < N; i += 2)
-            *reinterpret_cast<__nv_bfloat162 *>(&out.v[i]) = __floats2bfloat162_rn(v[i], v[i + 1]);
-    } else {
-#pragma unroll
-        for (int i = 0; i < N; ++i) out.v[i] = __float2bfloat16_rn(v[i]);
-    }
-}
-template <int N> __device__ __forceinline__ void pack_from_float(Pack<__half, N> &out, const float (&v)[N]) {
-    if constexpr (N % 2 == 0) {
-#pragma unroll
-        for (int i = 0; i < N; i += 2) *reinterpret_cast<__half2 *>(&out.v[i]) = __floats2half2_rn(v[i], v[i + 1]);
-    } else {
-#pragma unroll
-        for (int i = 0; i < N; ++i) out.v[i] = __float2half_rn(v[i]);
-    }
-}
-
-// A producer lane's copy slot: a fixed (time step within the stage, tile row, tensor); its global
-// source advances by a constant number of bytes from one stage to the next, so the per-stage
-// work of the producer is a wait, one expect_tx and a few address additions (no index decoding).
-struct CopySlot {
-    const uint8_t *src;
-    int64_t stage_step;   // bytes added to src per stage
-    uint32_t dst_off;     // byte offset inside a stage
-    uint32_t bytes;
-    int ts;               // time step within the stage; >= kTS marks an unused slot
-    int is_cprev;         // backward: the c[t-1] slab, absent for the step whose predecessor is c_init
-};
-constexpr int kSlotsPerLane = 4;
-
-template <bool B> using BoolC = std::integral_constant<bool, B>;
-
 template <typename T, typename TC, int V, int K>
-__global__ void __launch_bounds__(160) scan_fwd_pipe(const PipeArgs p) {
+__global__ void __launch_bounds__(160) scan_fwd_pipe(const __grid_constant__ ScanMaps maps, const PipeArgs p) {
     extern __shared__ __align__(128) uint8_t smem[];
     using G = GateFor<T>;
     const ScanArgs &a = p.a;
-    const int HW = p.c.hw, BR = p.c.br, TPR = p.c.tpr, NS = p.c.nstages;
+    const int HW = p.c.hw, BR = p.c.br, TPR = p.c.tpr, NS = p.c.nstages, SS = p.c.ss;
     const int tid = threadIdx.x;
     const int nthr_c = blockDim.x - 32;
     const int lane = tid & 31;
@@ -133,17 +56,19 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const PipeArgs p) {
     const int ht = blockIdx.x % p.c.nht, rt = blockIdx.x / p.c.nht;
     const int64_t dj0 = (int64_t)ht * HW;
     const int dir = (int)(dj0 / a.d);
+    const bool asc = (dir == 0);        // this tile walks time upwards
     const int64_t b0 = (int64_t)rt * BR;
     const int nrows = (int)min((int64_t)BR, a.B - b0);
     const int64_t L = a.L;
-    const int nst = (int)((L + kTS - 1) / kTS);
+    const int nst = (int)((L + SS - 1) / SS);
 
     const uint32_t bar_full = smem_u32(smem);
     const uint32_t bar_empty = bar_full + 8 * kMaxStages;
     const uint32_t u_slab = (uint32_t)HW * K * sizeof(T);   // bytes per (step,row)
     const uint32_t x_slab = has_x ? (uint32_t)HW * sizeof(T) : 0;
-    const uint32_t u_region = kTS * BR * u_slab;
-    const uint32_t stage_bytes = u_region + kTS * BR * x_slab;
+    const uint32_t u_region = align128(SS * BR * u_slab);
+    const uint32_t x_region = align128(SS * BR * x_slab);
+    const uint32_t stage_bytes = u_region + x_region;
     uint8_t *stage0 = smem + kBarBytes;
 
     if (tid == 0) {
@@ -156,49 +81,24 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const PipeArgs p) {
     __syncthreads();
 
     if (tid >= nthr_c) {
-        // ------------------------------ producer warp ------------------------------
-        const uint8_t *u = (const uint8_t *)a.u;
-        const uint8_t *x = (const uint8_t *)a.x;
-        const int ntens = has_x ? 2 : 1;
-        const int nslots = kTS * nrows * ntens;
-        const int per_lane = (nslots + 31) / 32;
-        if (per_lane > kSlotsPerLane) { if (lane == 0) atomicExch(p.err, 5); return; }  // host never picks such a tile
-        const int64_t tstride = (dir ? -1 : 1) * a.B * D * (int64_t)sizeof(T);   // bytes per time step (x)
-        CopySlot slot[kSlotsPerLane];
-#pragma unroll
-        for (int j = 0; j < kSlotsPerLane; ++j) {
-            const int idx = lane + 32 * j;
-            const int which = idx % ntens;
-            const int rr = (idx / ntens) % nrows;
-            const int ts = idx / (ntens * nrows);
-            const int64_t t = dir ? (L - 1 - ts) : ts;
-            const int64_t o = ((t * a.B + b0 + rr) * D + dj0) * (int64_t)sizeof(T);
-            slot[j].ts = (idx < nslots) ? ts : kTS;
-            slot[j].is_cprev = 0;
-            if (which == 0) {
-                slot[j].src = u + o * K; slot[j].stage_step = tstride * K * kTS;
-                slot[j].dst_off = (ts * BR + rr) * u_slab; slot[j].bytes = u_slab;
-            } else {
-                slot[j].src = x + o; slot[j].stage_step = tstride * kTS;
-                slot[j].dst_off = u_region + (ts * BR + rr) * x_slab; slot[j].bytes = x_slab;
-            }
-        }
+        // ------------------------------ producer (one thread) ------------------------------
+        if (lane != 0) return;
+        const int xu = (int)(dj0 * K * sizeof(T) / 8), xx = (int)(dj0 * sizeof(T) / 8);
         int s = 0;
         uint32_t ph = 1;   // the first pass over the ring finds every stage free
         for (int it = 0; it < nst; ++it) {
-            if (!mbar_wait_bounded(bar_empty + 8 * s, ph)) {
-                if (lane == 0) atomicExch(p.err, 1);
-                break;
-            }
-            const int steps = (int)min((int64_t)kTS, L - (int64_t)it * kTS);
+            if (!mbar_wait_bounded(bar_empty + 8 * s, ph)) { atomicExch(p.err, 1); break; }
             const uint32_t bar = bar_full + 8 * s;
-            if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)steps * nrows * (u_slab + x_slab));
-            __syncwarp();
-            const uint32_t sbase = smem_u32(stage0) + (uint32_t)s * stage_bytes;
-#pragma unroll
-            for (int j = 0; j < kSlotsPerLane; ++j) {
-                if (slot[j].ts < steps) bulk_copy_g2s(sbase + slot[j].dst_off, slot[j].src, slot[j].bytes, bar);
-                slot[j].src += slot[j].stage_step;
+            if (p.c.debug & 1) {
+                mbar_arrive(bar);
+            } else {
+                // ascending tiles take times [it*SS, it*SS+SS); descending ones the mirrored window,
+                // which may start below 0 (the box is zero-filled there)
+                const int t0 = asc ? it * SS : (int)(L - (int64_t)(it + 1) * SS);
+                mbar_arrive_expect_tx(bar, (uint32_t)SS * BR * (u_slab + x_slab));
+                const uint32_t sbase = smem_u32(stage0) + (uint32_t)s * stage_bytes;
+                tma_load_3d(sbase, &maps.u, bar, xu, (int)b0, t0);
+                if (has_x) tma_load_3d(sbase + u_region, &maps.x, bar, xx, (int)b0, t0);
             }
             if (++s == NS) { s = 0; ph ^= 1; }
         }
@@ -234,17 +134,17 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const PipeArgs p) {
     }
     const float scale = (float)a.scale_x;
     // Running pointers: one add per time step instead of rebuilding (t*B + b)*D + ... each step.
-    const int64_t t_first = dir ? (L - 1) : 0;
-    const int64_t ostep = dir ? -(a.B * D) : (a.B * D);
+    const int64_t t_first = asc ? 0 : (L - 1);
+    const int64_t ostep = asc ? (a.B * D) : -(a.B * D);
     T *hp = (T *)a.h + (t_first * a.B + b) * D + dj0 + hc;
     TC *cp = (TC *)a.c_hist + (has_hist ? (t_first * a.B + b) * D + dj0 + hc : 0);
-    const int64_t pstep = dir ? -a.B : a.B;
+    const int64_t pstep = asc ? a.B : -a.B;
     const uint8_t *pp = has_pad ? a.mask_pad + t_first * a.B + b : nullptr;
-    const uint32_t su = BR * u_slab, sx = BR * x_slab;
+    const int su = BR * (int)u_slab, sx = BR * (int)x_slab;      // bytes between time slabs of a stage
     const uint32_t u_off = r * u_slab + hc * K * sizeof(T);
     const uint32_t x_off = u_region + r * x_slab + hc * sizeof(T);
 
-    // pad flags of scan steps n_first .. n_first+kTS-1, one bit each; fetched two stages ahead
+    // pad flags of scan steps n_first .. n_first+3, one bit each; fetched two blocks ahead
     auto load_pad = [&](int64_t n_first) -> uint32_t {
         uint32_t bits = 0;
         if (has_pad && active) {
@@ -256,17 +156,18 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const PipeArgs p) {
         return bits;
     };
 
-    // One stage of kTS steps.  PAD / HIST / FULL are compile-time, so the unrolled body has no
-    // branch: padded steps keep c and emit 0 through selects.
-    auto stage = [&](const uint8_t *sb, uint32_t pad_bits, int steps, auto pad_c, auto hist_c, auto full_c) {
+    // One block of kTS steps.  ub / xb point at this thread's slice in the block's first time slab;
+    // dsu / dsx step to the next slab in scan order (negative for descending tiles).
+    auto block = [&](const uint8_t *ub, const uint8_t *xb, int dsu, int dsx, uint32_t pad_bits, int steps,
+                     auto pad_c, auto hist_c, auto full_c) {
         constexpr bool PAD = decltype(pad_c)::value, HIST = decltype(hist_c)::value, FULL = decltype(full_c)::value;
 #pragma unroll
         for (int ts = 0; ts < kTS; ++ts) {
             if (!FULL && ts >= steps) break;
             const bool pad = PAD && ((pad_bits >> ts) & 1u);
-            const Pack<T, V * K> up = *reinterpret_cast<const Pack<T, V * K> *>(sb + u_off + ts * su);
+            const Pack<T, V * K> up = *reinterpret_cast<const Pack<T, V * K> *>(ub + ts * dsu);
             Pack<T, V> xp;
-            if (has_x) xp = *reinterpret_cast<const Pack<T, V> *>(sb + x_off + ts * sx);
+            if (has_x) xp = *reinterpret_cast<const Pack<T, V> *>(xb + ts * dsx);
             float hv[V];
 #pragma unroll
             for (int i = 0; i < V; ++i) {
@@ -298,19 +199,25 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const PipeArgs p) {
         uint32_t pad0 = load_pad(0), pad1 = load_pad(kTS);
         int s = 0;
         uint32_t ph = 0;
+        int64_t n = 0;   // scan step of the next block
         for (int it = 0; it < nst; ++it) {
             if (!mbar_wait_bounded(bar_full + 8 * s, ph)) {
                 atomicExch(p.err, 2);
                 break;
             }
-            const uint32_t pad_cur = pad0;
-            pad0 = pad1;
-            pad1 = load_pad((int64_t)(it + 2) * kTS);
             const uint8_t *sb = stage0 + (size_t)s * stage_bytes;
-            const int64_t left = L - (int64_t)it * kTS;
-            if (active) {
-                if (left >= kTS) stage(sb, pad_cur, kTS, pad_c, hist_c, BoolC<true>{});
-                else stage(sb, pad_cur, (int)left, pad_c, hist_c, BoolC<false>{});
+            for (int q = 0; q < SS && n < L; q += kTS, n += kTS) {
+                const uint32_t pad_cur = pad0;
+                pad0 = pad1;
+                pad1 = load_pad(n + 2 * kTS);
+                if (active && !(p.c.debug & 2)) {
+                    const int slab = asc ? q : (SS - 1 - q);
+                    const uint8_t *ub = sb + u_off + slab * su;
+                    const uint8_t *xb = sb + x_off + slab * sx;
+                    const int64_t left = L - n;
+                    if (left >= kTS) block(ub, xb, asc ? su : -su, asc ? sx : -sx, pad_cur, kTS, pad_c, hist_c, BoolC<true>{});
+                    else block(ub, xb, asc ? su : -su, asc ? sx : -sx, pad_cur, (int)left, pad_c, hist_c, BoolC<false>{});
+                }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty + 8 * s);
@@ -337,11 +244,11 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const PipeArgs p) {
 //   cur <- gc*g1 + gg1*wc1 + gg2*wc2; accumulators gb1 += gg1, gb2 += gg2,
 //   gwc1 += gg1*c', gwc2 += gg2*c'.   c (this step's state) is recomputed from c'.
 template <typename T, typename TC, int V, int K>
-__global__ void __launch_bounds__(160) scan_bwd_pipe(const PipeArgs p) {
+__global__ void __launch_bounds__(160) scan_bwd_pipe(const __grid_constant__ ScanMaps maps, const PipeArgs p) {
     extern __shared__ __align__(128) uint8_t smem[];
     using G = GateFor<T>;
     const ScanArgs &a = p.a;
-    const int HW = p.c.hw, BR = p.c.br, TPR = p.c.tpr, NS = p.c.nstages;
+    const int HW = p.c.hw, BR = p.c.br, TPR = p.c.tpr, NS = p.c.nstages, SS = p.c.ss;
     const int tid = threadIdx.x;
     const int nthr_c = blockDim.x - 32;
     const int lane = tid & 31;
@@ -350,10 +257,11 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const PipeArgs p) {
     const int ht = blockIdx.x % p.c.nht, rt = blockIdx.x / p.c.nht;
     const int64_t dj0 = (int64_t)ht * HW;
     const int dir = (int)(dj0 / a.d);
+    const bool asc = (dir == 1);        // the backward walk of a reverse-direction tile goes up in time
     const int64_t b0 = (int64_t)rt * BR;
     const int nrows = (int)min((int64_t)BR, a.B - b0);
     const int64_t L = a.L;
-    const int nst = (int)((L + kTS - 1) / kTS);
+    const int nst = (int)((L + SS - 1) / SS);
 
     const uint32_t bar_full = smem_u32(smem);
     const uint32_t bar_empty = bar_full + 8 * kMaxStages;
@@ -361,10 +269,11 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const PipeArgs p) {
     const uint32_t x_slab = has_x ? (uint32_t)HW * sizeof(T) : 0;
     const uint32_t c_slab = (uint32_t)HW * sizeof(TC);
     const uint32_t g_slab = (uint32_t)HW * sizeof(T);
-    const uint32_t u_region = kTS * BR * u_slab;
-    const uint32_t x_region = kTS * BR * x_slab;
-    const uint32_t c_region = kTS * BR * c_slab;
-    const uint32_t stage_bytes = u_region + x_region + c_region + kTS * BR * g_slab;
+    const uint32_t u_region = align128(SS * BR * u_slab);
+    const uint32_t x_region = align128(SS * BR * x_slab);
+    const uint32_t c_region = align128(SS * BR * c_slab);
+    const uint32_t g_region = align128(SS * BR * g_slab);
+    const uint32_t stage_bytes = u_region + x_region + c_region + g_region;
     uint8_t *stage0 = smem + kBarBytes;
 
     if (tid == 0) {
@@ -384,73 +293,26 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const PipeArgs p) {
     for (int i = 0; i < V; ++i) { gwc1[i] = 0.f; gwc2[i] = 0.f; gb1[i] = 0.f; gb2[i] = 0.f; }
 
     if (tid >= nthr_c) {
-        // ------------------------------ producer warp ------------------------------
-        const uint8_t *u = (const uint8_t *)a.u;
-        const uint8_t *x = (const uint8_t *)a.x;
-        const uint8_t *chp = (const uint8_t *)a.c_hist;
-        const uint8_t *gh = (const uint8_t *)a.grad_h;
-        const int ntens = has_x ? 4 : 3;
-        const int nslots = kTS * nrows * ntens;
-        const int per_lane = (nslots + 31) / 32;
-        bool ok = per_lane <= kSlotsPerLane;
-        if (!ok && lane == 0) atomicExch(p.err, 6);   // host never picks such a tile
-        // backward step m visits time t = dir ? m : L-1-m; its predecessor state sits one step earlier
-        // in the forward's scan order, i.e. at t + (dir ? 1 : -1)
-        const int64_t tsign = dir ? 1 : -1;
-        const int64_t row_t = a.B * D * (int64_t)sizeof(T);    // bytes per time step, T tensors
-        const int64_t row_c = a.B * D * (int64_t)sizeof(TC);
-        CopySlot slot[kSlotsPerLane];
-#pragma unroll
-        for (int j = 0; j < kSlotsPerLane; ++j) {
-            const int idx = lane + 32 * j;
-            const int which = idx % ntens;
-            const int rr = (idx / ntens) % nrows;
-            const int ts = idx / (ntens * nrows);
-            const int64_t t = dir ? ts : (L - 1 - ts);
-            const int64_t e = (t * a.B + b0 + rr) * D + dj0;   // element offset of the row slab
-            slot[j].ts = (ok && idx < nslots) ? ts : kTS;
-            slot[j].is_cprev = 0;
-            if (which == 0) {
-                slot[j].src = u + e * K * (int64_t)sizeof(T); slot[j].stage_step = tsign * row_t * K * kTS;
-                slot[j].dst_off = (ts * BR + rr) * u_slab; slot[j].bytes = u_slab;
-            } else if (which == 1) {
-                slot[j].src = gh + e * (int64_t)sizeof(T); slot[j].stage_step = tsign * row_t * kTS;
-                slot[j].dst_off = u_region + x_region + c_region + (ts * BR + rr) * g_slab; slot[j].bytes = g_slab;
-            } else if (which == 2) {
-                // c at the forward's previous scan step: one time step further along the backward walk
-                slot[j].src = chp + e * (int64_t)sizeof(TC) + tsign * row_c; slot[j].stage_step = tsign * row_c * kTS;
-                slot[j].dst_off = u_region + x_region + (ts * BR + rr) * c_slab; slot[j].bytes = c_slab;
-                slot[j].is_cprev = 1;
-            } else {
-                slot[j].src = x + e * (int64_t)sizeof(T); slot[j].stage_step = tsign * row_t * kTS;
-                slot[j].dst_off = u_region + (ts * BR + rr) * x_slab; slot[j].bytes = x_slab;
+        // ------------------------------ producer (one thread) ------------------------------
+        if (lane == 0) {
+            const int xu = (int)(dj0 * K * sizeof(T) / 8), xx = (int)(dj0 * sizeof(T) / 8);
+            const int xc = (int)(dj0 * sizeof(TC) / 8);
+            int s = 0;
+            uint32_t ph = 1;
+            for (int it = 0; it < nst; ++it) {
+                if (!mbar_wait_bounded(bar_empty + 8 * s, ph)) { atomicExch(p.err, 3); break; }
+                const uint32_t bar = bar_full + 8 * s;
+                const int t0 = asc ? it * SS : (int)(L - (int64_t)(it + 1) * SS);
+                mbar_arrive_expect_tx(bar, (uint32_t)SS * BR * (u_slab + x_slab + c_slab + g_slab));
+                const uint32_t sbase = smem_u32(stage0) + (uint32_t)s * stage_bytes;
+                tma_load_3d(sbase, &maps.u, bar, xu, (int)b0, t0);
+                if (has_x) tma_load_3d(sbase + u_region, &maps.x, bar, xx, (int)b0, t0);
+                // the state BEFORE each step: one time step further along this walk (out-of-range rows,
+                // i.e. the predecessor of the sequence start, are zero-filled and replaced by c_init)
+                tma_load_3d(sbase + u_region + x_region, &maps.c, bar, xc, (int)b0, asc ? t0 + 1 : t0 - 1);
+                tma_load_3d(sbase + u_region + x_region + c_region, &maps.g, bar, xx, (int)b0, t0);
+                if (++s == NS) { s = 0; ph ^= 1; }
             }
-        }
-        int s = 0;
-        uint32_t ph = 1;
-        for (int it = 0; it < nst && ok; ++it) {
-            if (!mbar_wait_bounded(bar_empty + 8 * s, ph)) {
-                if (lane == 0) atomicExch(p.err, 3);
-                break;
-            }
-            const int64_t left = L - (int64_t)it * kTS;
-            const int steps = (int)min((int64_t)kTS, left);
-            const int last_ts = (left <= kTS) ? (int)left - 1 : kTS;   // the step that starts from c_init
-            const uint32_t bar = bar_full + 8 * s;
-            if (lane == 0) {
-                uint32_t bytes = (uint32_t)steps * nrows * (u_slab + x_slab + c_slab + g_slab);
-                if (left <= kTS) bytes -= (uint32_t)nrows * c_slab;
-                mbar_arrive_expect_tx(bar, bytes);
-            }
-            __syncwarp();
-            const uint32_t sbase = smem_u32(stage0) + (uint32_t)s * stage_bytes;
-#pragma unroll
-            for (int j = 0; j < kSlotsPerLane; ++j) {
-                if (slot[j].ts < steps && !(slot[j].is_cprev && slot[j].ts == last_ts))
-                    bulk_copy_g2s(sbase + slot[j].dst_off, slot[j].src, slot[j].bytes, bar);
-                slot[j].src += slot[j].stage_step;
-            }
-            if (++s == NS) { s = 0; ph ^= 1; }
         }
     } else {
         // -------------------------------- consumers --------------------------------
@@ -478,14 +340,14 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const PipeArgs p) {
         }
         const float scale = (float)a.scale_x;
         // Backward step m visits the forward's scan step n = L-1-m, i.e. time t = dir ? m : L-1-m.
-        const int64_t t_first = dir ? 0 : (L - 1);
-        const int64_t ostep = dir ? (a.B * D) : -(a.B * D);
+        const int64_t t_first = asc ? 0 : (L - 1);
+        const int64_t ostep = asc ? (a.B * D) : -(a.B * D);
         const int64_t o_first = (t_first * a.B + b) * D + dj0 + hc;
         T *gup = (T *)a.grad_u + o_first * K;
         T *gxp = (T *)a.grad_x + (has_x ? o_first : 0);
-        const int64_t pstep = dir ? a.B : -a.B;
+        const int64_t pstep = asc ? a.B : -a.B;
         const uint8_t *pp = has_pad ? a.mask_pad + t_first * a.B + b : nullptr;
-        const uint32_t su = BR * u_slab, sx = BR * x_slab, sc = BR * c_slab, sg = BR * g_slab;
+        const int su = BR * (int)u_slab, sx = BR * (int)x_slab, sc = BR * (int)c_slab, sg = BR * (int)g_slab;
         const uint32_t u_off = r * u_slab + hc * K * sizeof(T);
         const uint32_t x_off = u_region + r * x_slab + hc * sizeof(T);
         const uint32_t c_off = u_region + x_region + r * c_slab + hc * sizeof(TC);
@@ -502,20 +364,21 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const PipeArgs p) {
             return bits;
         };
 
-        // One stage.  LAST marks the final stage (ragged, and holding the step whose predecessor
-        // state is c_init); all other stages are full and branch-free.
-        auto stage = [&](const uint8_t *sb, uint32_t pad_bits, int steps, auto pad_c, auto last_c) {
+        // One block of kTS steps.  LAST marks the final block (ragged, and holding the step whose
+        // predecessor state is c_init); all other blocks are full and branch-free.
+        auto block = [&](const uint8_t *sb, int slab, int dslab, uint32_t pad_bits, int steps, auto pad_c, auto last_c) {
             constexpr bool PAD = decltype(pad_c)::value, LAST = decltype(last_c)::value;
 #pragma unroll
             for (int ts = 0; ts < kTS; ++ts) {
                 if (LAST && ts >= steps) break;
                 const bool pad = PAD && ((pad_bits >> ts) & 1u);
                 const bool at_start = LAST && (ts == steps - 1);
-                const Pack<T, V * K> up = *reinterpret_cast<const Pack<T, V * K> *>(sb + u_off + ts * su);
-                const Pack<T, V> ghp = *reinterpret_cast<const Pack<T, V> *>(sb + g_off + ts * sg);
+                const int sl = slab + ts * dslab;
+                const Pack<T, V * K> up = *reinterpret_cast<const Pack<T, V * K> *>(sb + u_off + sl * su);
+                const Pack<T, V> ghp = *reinterpret_cast<const Pack<T, V> *>(sb + g_off + sl * sg);
                 Pack<T, V> xp;
-                if (has_x) xp = *reinterpret_cast<const Pack<T, V> *>(sb + x_off + ts * sx);
-                const Pack<TC, V> cpp = *reinterpret_cast<const Pack<TC, V> *>(sb + c_off + ts * sc);
+                if (has_x) xp = *reinterpret_cast<const Pack<T, V> *>(sb + x_off + sl * sx);
+                const Pack<TC, V> cpp = *reinterpret_cast<const Pack<TC, V> *>(sb + c_off + sl * sc);
                 float guv[V * K], gxv_[V];
 #pragma unroll
                 for (int i = 0; i < V; ++i) {
@@ -567,19 +430,23 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const PipeArgs p) {
             uint32_t pad0 = load_pad(0), pad1 = load_pad(kTS);
             int s = 0;
             uint32_t ph = 0;
+            int64_t m = 0;   // backward step of the next block
             for (int it = 0; it < nst; ++it) {
                 if (!mbar_wait_bounded(bar_full + 8 * s, ph)) {
                     atomicExch(p.err, 4);
                     break;
                 }
-                const uint32_t pad_cur = pad0;
-                pad0 = pad1;
-                pad1 = load_pad((int64_t)(it + 2) * kTS);
                 const uint8_t *sb = stage0 + (size_t)s * stage_bytes;
-                const int64_t left = L - (int64_t)it * kTS;   // steps left including this stage
-                if (active) {
-                    if (left > kTS) stage(sb, pad_cur, kTS, pad_c, BoolC<false>{});
-                    else stage(sb, pad_cur, (int)left, pad_c, BoolC<true>{});
+                for (int q = 0; q < SS && m < L; q += kTS, m += kTS) {
+                    const uint32_t pad_cur = pad0;
+                    pad0 = pad1;
+                    pad1 = load_pad(m + 2 * kTS);
+                    if (active) {
+                        const int slab = asc ? q : (SS - 1 - q);
+                        const int64_t left = L - m;   // steps left including this block
+                        if (left > kTS) block(sb, slab, asc ? 1 : -1, pad_cur, kTS, pad_c, BoolC<false>{});
+                        else block(sb, slab, asc ? 1 : -1, pad_cur, (int)left, pad_c, BoolC<true>{});
+                    }
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_empty + 8 * s);
@@ -620,7 +487,7 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const PipeArgs p) {
 }
 
 // ---------------------------------------------------------------------------------------
-// Host side: tile selection and dispatch
+// Host side: tile selection, tensor maps and dispatch
 // ---------------------------------------------------------------------------------------
 static int g_num_sms = 0;
 static int num_sms() {
@@ -640,13 +507,42 @@ static int env_int(const char *name, int dflt) {
     return (e && *e) ? atoi(e) : dflt;
 }
 
+static PFN_cuTensorMapEncodeTiled_v12000 scan_encode_fn() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    if (!fn) {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+    }
+    return fn;
+}
+
+// 3-D map over a (L, B, row) tensor whose rows are row_bytes long, in 8-byte elements:
+// dims (row_bytes/8, B, L), box (box_bytes/8, br, ss), no swizzle, out-of-range reads give zeros.
+static int make_scan_map(CUtensorMap *map, const void *base, int64_t row_bytes, int64_t B, int64_t L,
+                         int64_t box_bytes, int br, int ss) {
+    auto fn = scan_encode_fn();
+    if (!fn) return set_error(SRU_ERR_CUDA, "cuTensorMapEncodeTiled entry point not found");
+    cuuint64_t dims[3] = {(cuuint64_t)(row_bytes / 8), (cuuint64_t)B, (cuuint64_t)L};
+    cuuint64_t strides[2] = {(cuuint64_t)row_bytes, (cuuint64_t)(row_bytes * B)};
+    cuuint32_t box[3] = {(cuuint32_t)(box_bytes / 8), (cuuint32_t)br, (cuuint32_t)ss};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(SRU_ERR_CUDA, "cuTensorMapEncodeTiled (scan) failed with %d", (int)r);
+    return 0;
+}
+
 // Chooses V, the tile and the ring.  Returns false when the shape is not eligible.
 static bool choose_tile(int64_t L, int64_t B, int64_t d, int dirs, int k, int skip_type, int dtype,
                         int c_dtype, bool backward, TileCfg *out) {
     const int s = (int)dtype_size(dtype);
     if (dtype == SRU_F64 || s == 0) return false;
     const int granule = 16 / s;  // elements per 16 bytes
-    if (d % granule != 0 || L < 1 || B < 1) return false;
+    if (d % granule != 0 || L < 1 || B < 1 || L > 0x7fffff00 || B > 0x7fffffff) return false;
     const int64_t D = d * dirs, ncols = B * D;
     const int sms = num_sms();
     const int vmax = 4, vmin = 2;
@@ -660,24 +556,37 @@ static bool choose_tile(int64_t L, int64_t B, int64_t d, int dirs, int k, int sk
     int ntc = (ncols / ((int64_t)v * 64) >= (int64_t)sms) ? 64 : 32;
     ntc = env_int("SRU_B200_SCAN_THREADS", ntc);
     if (ntc < 32 || ntc > 128 || ntc % 32) return false;
-    // hidden width of the tile: largest divisor of d, multiple of the granule, <= v*ntc
+    // hidden width of the tile: largest divisor of d, multiple of the granule, <= v*ntc, and with a
+    // U slab of at most 2048 bytes (256 eight-byte elements, the widest box the tensor map takes)
     int hw = 0;
     for (int64_t cand = (int64_t)v * ntc; cand >= granule; cand -= granule) {
-        if (d % cand == 0) { hw = (int)cand; break; }
+        if (d % cand == 0 && cand * k * s <= 2048) { hw = (int)cand; break; }
     }
     if (hw == 0) return false;
     const int tpr = hw / v;
     int br = (int)std::min<int64_t>(B, std::max(1, ntc / tpr));
-    // the producer warp keeps at most kSlotsPerLane copies per lane and stage: kTS * br * tensors <= 128
-    br = std::min(br, (32 * kSlotsPerLane) / (kTS * (backward ? 4 : 2)));
     const int cthreads = ((br * tpr + 31) / 32) * 32;
     if (cthreads > 128) return false;
     const bool has_x = (k == 3 && skip_type == 1);
     const int sc = (int)dtype_size(c_dtype);
     size_t per_row_step = (size_t)hw * (k * s + (has_x ? s : 0));
     if (backward) per_row_step += (size_t)hw * (sc + s);
-    const size_t stage_bytes = (size_t)kTS * br * per_row_step;
-    // ring: about 72 KB per CTA slot, shared by the CTAs expected on one SM
+    // time steps per stage: one request should carry about 16 KB (fewer barrier round trips per
+    // step), as long as three stages still fit the CTA's share of shared memory
+    const int64_t nctas0 = ((B + br - 1) / br) * (D / hw);
+    const int cps0 = (int)std::min<int64_t>(std::max<int64_t>(1, (nctas0 + sms - 1) / sms), 2048 / (cthreads + 32));
+    const size_t ring0 = std::min<size_t>(200 * 1024 / cps0, 96 * 1024);
+    int ss = kTS;
+    while (ss < 32 && (size_t)ss * br * per_row_step < 16 * 1024 && (size_t)(2 * ss) * br * per_row_step * 3 <= ring0) ss *= 2;
+    ss = env_int("SRU_B200_SCAN_SS", ss);
+    if (ss < kTS || ss > 64 || ss % kTS) return false;
+    auto stage_size = [&](int steps) {
+        size_t t = align128((uint32_t)(steps * br * hw * k * s)) + align128((uint32_t)(has_x ? steps * br * hw * s : 0));
+        if (backward) t += align128((uint32_t)(steps * br * hw * sc)) + align128((uint32_t)(steps * br * hw * s));
+        return t;
+    };
+    const size_t stage_bytes = stage_size(ss);
+    // ring: shared by the CTAs expected on one SM
     const int64_t nctas = ((B + br - 1) / br) * (D / hw);
     int cta_per_sm = (int)std::min<int64_t>(std::max<int64_t>(1, (nctas + sms - 1) / sms), 2048 / (cthreads + 32));
     size_t ring = std::min<size_t>(200 * 1024 / cta_per_sm, 96 * 1024);
@@ -694,7 +603,8 @@ static bool choose_tile(int64_t L, int64_t B, int64_t d, int dirs, int k, int sk
     }
     out->hw = hw; out->br = br; out->tpr = tpr;
     out->nht = (int)(D / hw); out->nrt = (int)((B + br - 1) / br);
-    out->nstages = ns; out->v = v; out->threads = cthreads + 32; out->smem = smem;
+    out->nstages = ns; out->ss = ss; out->v = v; out->debug = env_int("SRU_B200_SCAN_DEBUG", 0);
+    out->threads = cthreads + 32; out->smem = smem;
     return nctas <= 0x7fffffff;
 }
 
@@ -715,52 +625,72 @@ size_t pipelined_workspace_bytes(int64_t L, int64_t B, int64_t d, int dirs, int 
 }
 
 template <typename T, typename TC, int V, int K>
-static int launch_t(const PipeArgs &p, bool backward, cudaStream_t st) {
+static int launch_t(const ScanMaps &maps, const PipeArgs &p, bool backward, cudaStream_t st) {
     auto fwd = scan_fwd_pipe<T, TC, V, K>;
     auto bwd = scan_bwd_pipe<T, TC, V, K>;
     const void *fn = backward ? (const void *)bwd : (const void *)fwd;
     if (p.c.smem > 48 * 1024)
         SRUB_CUDA_CHECK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.c.smem));
     const unsigned grid = (unsigned)((int64_t)p.c.nht * p.c.nrt);
-    if (backward) bwd<<<grid, p.c.threads, p.c.smem, st>>>(p);
-    else fwd<<<grid, p.c.threads, p.c.smem, st>>>(p);
+    if (backward) bwd<<<grid, p.c.threads, p.c.smem, st>>>(maps, p);
+    else fwd<<<grid, p.c.threads, p.c.smem, st>>>(maps, p);
     SRUB_CUDA_CHECK(cudaGetLastError());
     return 1;
 }
 
 template <typename T, typename TC, int K>
-static int launch_v(const PipeArgs &p, bool backward, cudaStream_t st) {
+static int launch_v(const ScanMaps &maps, const PipeArgs &p, bool backward, cudaStream_t st) {
     switch (p.c.v) {
-        case 2: return launch_t<T, TC, 2, K>(p, backward, st);
-        case 4: return launch_t<T, TC, 4, K>(p, backward, st);
+        case 2: return launch_t<T, TC, 2, K>(maps, p, backward, st);
+        case 4: return launch_t<T, TC, 4, K>(maps, p, backward, st);
     }
     return set_error(SRU_ERR_UNSUPPORTED, "columns per thread %d", p.c.v);
 }
 
 template <typename T, typename TC>
-static int launch_k(const PipeArgs &p, bool backward, cudaStream_t st) {
-    return p.a.k == 3 ? launch_v<T, TC, 3>(p, backward, st) : launch_v<T, TC, 4>(p, backward, st);
+static int launch_k(const ScanMaps &maps, const PipeArgs &p, bool backward, cudaStream_t st) {
+    return p.a.k == 3 ? launch_v<T, TC, 3>(maps, p, backward, st) : launch_v<T, TC, 4>(maps, p, backward, st);
 }
 
 int launch_scan_pipelined(const ScanArgs &a, bool backward, cudaStream_t st) {
     if (!pipelined_eligible(a)) return 0;
-    PipeArgs p;
-    p.a = a;
-    if (!choose_tile(a.L, a.B, a.d, a.dirs, a.k, a.skip_type, a.dtype, a.c_dtype, backward, &p.c)) return 0;
-    // bulk copies need 16-byte aligned sources; packed stores need V*sizeof(T) alignment
+    // tensor maps need 16-byte aligned bases; packed stores need V*sizeof(T) alignment
     const void *ptrs[] = {a.u, a.x, a.h, a.c_hist, a.grad_h, a.grad_u, a.grad_x, a.c_last, a.c_init,
                           a.grad_last, a.grad_init, a.mask_c};
     for (const void *q : ptrs)
         if (q && !aligned16(q)) return 0;
-    p.err = device_error_flag();
-    if (!p.err) return set_error(SRU_ERR_CUDA, "device error flag unavailable");
+    int *err = device_error_flag();
+    if (!err) return set_error(SRU_ERR_CUDA, "device error flag unavailable");
+    PipeArgs p;
+    p.a = a;
+    if (!choose_tile(a.L, a.B, a.d, a.dirs, a.k, a.skip_type, a.dtype, a.c_dtype, backward, &p.c)) return 0;
+    p.err = err;
+
+    // The tensor-map encoder is a driver entry point: make sure this thread has the primary context.
+    SRUB_CUDA_CHECK(cudaFree(nullptr));
+    const int64_t s = (int64_t)dtype_size(a.dtype), sc = (int64_t)dtype_size(a.c_dtype);
+    const int64_t D = (int64_t)a.d * a.dirs;
+    ScanMaps maps;
+    memset(&maps, 0, sizeof(maps));
+    int rc = make_scan_map(&maps.u, a.u, D * a.k * s, a.B, a.L, (int64_t)p.c.hw * a.k * s, p.c.br, p.c.ss);
+    if (rc) return rc;
+    if (a.k == 3) {
+        rc = make_scan_map(&maps.x, a.x, D * s, a.B, a.L, (int64_t)p.c.hw * s, p.c.br, p.c.ss);
+        if (rc) return rc;
+    }
+    if (backward) {
+        rc = make_scan_map(&maps.c, a.c_hist, D * sc, a.B, a.L, (int64_t)p.c.hw * sc, p.c.br, p.c.ss);
+        if (rc) return rc;
+        rc = make_scan_map(&maps.g, a.grad_h, D * s, a.B, a.L, (int64_t)p.c.hw * s, p.c.br, p.c.ss);
+        if (rc) return rc;
+    }
+
     const int dt = a.dtype, ct = a.c_dtype;
-    int rc;
-    if (dt == SRU_F32 && ct == SRU_F32) rc = launch_k<float, float>(p, backward, st);
-    else if (dt == SRU_F16 && ct == SRU_F16) rc = launch_k<__half, __half>(p, backward, st);
-    else if (dt == SRU_F16 && ct == SRU_F32) rc = launch_k<__half, float>(p, backward, st);
-    else if (dt == SRU_BF16 && ct == SRU_BF16) rc = launch_k<__nv_bfloat16, __nv_bfloat16>(p, backward, st);
-    else if (dt == SRU_BF16 && ct == SRU_F32) rc = launch_k<__nv_bfloat16, float>(p, backward, st);
+    if (dt == SRU_F32 && ct == SRU_F32) rc = launch_k<float, float>(maps, p, backward, st);
+    else if (dt == SRU_F16 && ct == SRU_F16) rc = launch_k<__half, __half>(maps, p, backward, st);
+    else if (dt == SRU_F16 && ct == SRU_F32) rc = launch_k<__half, float>(maps, p, backward, st);
+    else if (dt == SRU_BF16 && ct == SRU_BF16) rc = launch_k<__nv_bfloat16, __nv_bfloat16>(maps, p, backward, st);
+    else if (dt == SRU_BF16 && ct == SRU_F32) rc = launch_k<__nv_bfloat16, float>(maps, p, backward, st);
     else return set_error(SRU_ERR_UNSUPPORTED, "dtype %d with c_dtype %d", dt, ct);
     if (rc < 0) return rc;
     if (backward) {
