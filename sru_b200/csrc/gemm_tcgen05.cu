@@ -30,6 +30,8 @@
 #include <cudaTypedefs.h>
 
 #include <algorithm>
+#include <cstdlib>
+#include <cstring>
 
 #include "common.cuh"
 
@@ -296,6 +298,217 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
+// =========================================================================================
+// Two-SM variant (cta_group::2).  A cluster of two CTAs on neighbouring SMs computes a
+// 256 x 256 tile: each CTA loads its own 128 rows of A and its own 128-column half of B into
+// its shared memory, the leader CTA (cluster rank 0) issues tcgen05.mma.cta_group::2 with
+// M = 256, and each SM's tensor core reads only half of the B operand from its own shared
+// memory - the single-CTA kernel above is limited by that shared-memory read traffic (12 KB per
+// 64 tensor cycles).  Each CTA's tensor memory holds the accumulator rows of its own 128 rows.
+//   full[s]      lives in the leader; both CTAs' TMA requests complete on it (the .cta_group::2
+//                form of the load addresses the leader's barrier), the leader's producer
+//                announces the bytes of both.
+//   empty[s], tmem_full[a]   one per CTA; tcgen05.commit from the leader arrives on both.
+//   tmem_empty[a] lives in the leader; the four epilogue warps of each CTA arrive on it (the
+//                peer's through its cluster-mapped address).
+// No load is shared between CTAs: every TMA request lands in the shared memory of the CTA that
+// issued it.
+constexpr int kStages2 = 6;
+constexpr int kAStage2 = 128 * BK * 2;   // 16 KB: this CTA's 128 rows of A
+constexpr int kBStage2 = 128 * BK * 2;   // 16 KB: this CTA's 128 columns of B
+constexpr int kSmemBytes2 = kStages2 * (kAStage2 + kBStage2) + 1024 + 256;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// TMA load of the pair form: data into THIS CTA's shared memory, completion bytes on the barrier
+// at the same offset in the leader CTA (rank bit of the barrier address cleared).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar & 0xFEFFFFFFu), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t slot_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {   // arrives on `bar` in both CTAs
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(bar), "h"((uint16_t)3)
+        : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                        const GemmArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *smem_a = smem;
+    uint8_t *smem_b = smem + kStages2 * kAStage2;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kStages2 * (kAStage2 + kBStage2));
+    const uint32_t bar_full = smem_u32(bars);              // [kStages2]  (used in the leader)
+    const uint32_t bar_empty = bar_full + 8 * kStages2;    // [kStages2]  (one per CTA)
+    const uint32_t bar_tfull = bar_empty + 8 * kStages2;   // [2]         (one per CTA)
+    const uint32_t bar_tempty = bar_tfull + 16;            // [2]         (used in the leader)
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages2 + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();               // 0 = leader
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    const int ntiles = g.tiles_m * g.tiles_n;              // tiles of 256 x 256
+    const int nkb = (int)((g.K + BK - 1) / BK);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages2; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(bar_tfull + 8 * i, 1); mbar_init(bar_tempty + 8 * i, 8); }
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc2(smem_u32(tmem_slot), kTmemCols);
+        tmem_relinquish2();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();     // both CTAs' barriers exist before anything signals across the pair
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------- TMA producer (both CTAs) -------------------------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = pair; tile < ntiles && ok; tile += npairs) {
+                const int mb = tile / g.tiles_n, nb = tile % g.tiles_n;
+                const int m0 = mb * 256 + (int)rank * 128;      // this CTA's rows of A
+                const int n0 = nb * BN + (int)rank * 128;       // this CTA's columns of B
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1)) { atomicExch(g.err, 21); ok = false; break; }
+                    const uint32_t full = bar_full + 8 * stage;
+                    if (rank == 0) mbar_arrive_expect_tx(full, 2 * (kAStage2 + kBStage2));
+                    const uint32_t sa = smem_u32(smem_a + stage * kAStage2);
+                    const uint32_t sb = smem_u32(smem_b + stage * kBStage2);
+                    if (!g.a_mn) {
+                        tma_load_2d_pair(sa, &map_a, full, kb * BK, m0);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) tma_load_2d_pair(sa + j * 8192, &map_a, full, m0 + j * 64, kb * BK);
+                    }
+                    if (!g.b_mn) {
+                        tma_load_2d_pair(sb, &map_b, full, kb * BK, n0);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) tma_load_2d_pair(sb + j * 8192, &map_b, full, n0 + j * 64, kb * BK);
+                    }
+                    if (++stage == kStages2) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    }
+    else if (warp == 1) {
+        // ------------------------------ MMA issuer (leader CTA only) ------------------------------
+        if (lane == 0 && rank == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            int it = 0;
+            const uint32_t a_step = g.a_mn ? 2048u : 32u, b_step = g.b_mn ? 2048u : 32u;
+            const uint32_t a_lbo = g.a_mn ? 8192u : 16u, b_lbo = g.b_mn ? 8192u : 16u;
+            for (int tile = pair; tile < ntiles && ok; tile += npairs, ++it) {
+                const int acc = it & 1;
+                const uint32_t acc_phase = (it >> 1) & 1;
+                if (!mbar_wait_bounded(bar_tempty + 8 * acc, acc_phase ^ 1)) { atomicExch(g.err, 22); break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!mbar_wait_bounded(bar_full + 8 * stage, phase)) { atomicExch(g.err, 23); ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem_a + stage * kAStage2);
+                    const uint32_t sb = smem_u32(smem_b + stage * kBStage2);
+#pragma unroll
+                    for (int k16 = 0; k16 < BK / 16; ++k16) {
+                        const uint64_t ad = make_desc(sa + k16 * a_step, a_lbo, 1024);
+                        const uint64_t bd = make_desc(sb + k16 * b_step, b_lbo, 1024);
+                        tc_mma_pair(d_tmem, ad, bd, g.idesc, (kb | k16) ? 1u : 0u);
+                    }
+                    tc_commit_pair(bar_empty + 8 * stage);    // frees the stage in both CTAs
+                    if (++stage == kStages2) { stage = 0; phase ^= 1; }
+                }
+                if (ok) tc_commit_pair(bar_tfull + 8 * acc);   // accumulators complete in both CTAs
+            }
+        }
+    } else {
+        // ------------------------------ epilogue (both CTAs, own rows) ------------------------------
+        const int q = warp & 3;
+        const uint32_t tempty_leader = map_to_cta(bar_tempty, 0);
+        int it = 0;
+        for (int tile = pair; tile < ntiles; tile += npairs, ++it) {
+            const int mb = tile / g.tiles_n, nb = tile % g.tiles_n;
+            const int acc = it & 1;
+            const uint32_t acc_phase = (it >> 1) & 1;
+            if (!mbar_wait_bounded(bar_tfull + 8 * acc, acc_phase)) { if (lane == 0) atomicExch(g.err, 24); break; }
+            tc_fence_after();
+            const int64_t row = (int64_t)mb * 256 + rank * 128 + q * 32 + lane;
+            const int64_t col_base = (int64_t)nb * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                const int64_t col0 = col_base + c * 32;
+                if (col0 >= g.N) break;
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, r);
+                tmem_ld_wait();
+                if (row < g.M) {
+                    if (g.c_dtype == SRU_BF16) epilogue_chunk<__nv_bfloat16>(g, r, row, col0);
+                    else if (g.c_dtype == SRU_F16) epilogue_chunk<__half>(g, r, row, col0);
+                    else epilogue_chunk<float>(g, r, row, col0);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty_leader + 8 * acc);
+        }
+    }
+
+    // -------------------------------- teardown --------------------------------
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();     // neither CTA leaves while its pair may still signal its barriers
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc2(tmem_base, kTmemCols);
+    }
+}
+
 // ---- host side --------------------------------------------------------------------------
 PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
     static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
@@ -355,14 +568,24 @@ extern "C" int sru_b200_gemm(void *c, const void *a, const void *b, const float 
     // worker, for instance) gets it bound by this no-op runtime call.
     SRUB_CUDA_CHECK(cudaFree(nullptr));
 
+    // Pair kernel (two SMs per 256 x 256 tile) once there are enough such tiles to fill the GPU;
+    // SRU_B200_GEMM_2SM=0/1 overrides.
+    int dev = 0, sms = 148;
+    SRUB_CUDA_CHECK(cudaGetDevice(&dev));
+    SRUB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const int64_t tiles256 = ((m + 255) / 256) * ((n + BN - 1) / BN);
+    bool two_sm = tiles256 >= sms / 2;
+    if (const char *e = getenv("SRU_B200_GEMM_2SM")) two_sm = (*e == '1');
+
     CUtensorMap map_a, map_b;
     int rc;
     // A: K-major stored (M,K) -> inner K, box 64 x 128.  MN-major stored (K,M) -> inner M, box 64 x 64.
     if (!trans_a) rc = make_map(&map_a, a, ab_dtype, k_dim, m, lda, BK, BM);
     else rc = make_map(&map_a, a, ab_dtype, m, k_dim, lda, 64, BK);
     if (rc) return rc;
-    // B: K-major stored (N,K) -> inner K, box 64 x 256.  MN-major stored (K,N) -> inner N, box 64 x 64.
-    if (trans_b) rc = make_map(&map_b, b, ab_dtype, k_dim, n, ldb, BK, BN);
+    // B: K-major stored (N,K) -> inner K, box 64 x 256 (64 x 128 per CTA of a pair).
+    // MN-major stored (K,N) -> inner N, box 64 x 64.
+    if (trans_b) rc = make_map(&map_b, b, ab_dtype, k_dim, n, ldb, BK, two_sm ? 128 : BN);
     else rc = make_map(&map_b, b, ab_dtype, n, k_dim, ldb, 64, BK);
     if (rc) return rc;
 
@@ -376,24 +599,40 @@ extern "C" int sru_b200_gemm(void *c, const void *a, const void *b, const float 
     // (bits 15, 16), N/8 (bits 17-22), M/16 (bits 24-28)
     g.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)g.a_mn << 15) | ((uint32_t)g.b_mn << 16) |
               ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-    g.tiles_m = (int)((m + BM - 1) / BM);
+    const int tile_m = two_sm ? 256 : BM;
+    if (two_sm) g.idesc = (g.idesc & ~(0x1Fu << 24)) | ((uint32_t)(256 >> 4) << 24);
+    g.tiles_m = (int)((m + tile_m - 1) / tile_m);
     g.tiles_n = (int)((n + BN - 1) / BN);
     g.err = device_error_flag();
     if (!g.err) return set_error(SRU_ERR_CUDA, "device error flag unavailable");
     const int64_t ntiles = (int64_t)g.tiles_m * g.tiles_n;
     if (ntiles > 0x7fffffff) return set_error(SRU_ERR_BAD_ARG, "too many gemm tiles");
 
-    int dev = 0, sms = 148;
-    SRUB_CUDA_CHECK(cudaGetDevice(&dev));
-    SRUB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     static bool attr_set[64] = {false};
     if (dev < 64 && !attr_set[dev]) {
         SRUB_CUDA_CHECK(cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              kSmemBytes));
+        SRUB_CUDA_CHECK(cudaFuncSetAttribute(gemm_tcgen05_2sm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             kSmemBytes2));
         attr_set[dev] = true;
     }
-    const unsigned grid = (unsigned)std::min<int64_t>(ntiles, sms);
-    gemm_tcgen05_kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(map_a, map_b, g);
+    if (two_sm) {
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3(2u * (unsigned)std::min<int64_t>(ntiles, sms / 2), 1, 1);
+        cfg.blockDim = dim3(kThreads, 1, 1);
+        cfg.dynamicSmemBytes = kSmemBytes2;
+        cfg.stream = static_cast<cudaStream_t>(stream);
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        SRUB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tcgen05_2sm_kernel, map_a, map_b, g));
+    } else {
+        const unsigned grid = (unsigned)std::min<int64_t>(ntiles, sms);
+        gemm_tcgen05_kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(map_a, map_b, g);
+    }
     SRUB_CUDA_CHECK(cudaGetLastError());
     return 0;
 }
