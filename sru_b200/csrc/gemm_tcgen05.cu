@@ -313,10 +313,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 //                peer's through its cluster-mapped address).
 // No load is shared between CTAs: every TMA request lands in the shared memory of the CTA that
 // issued it.
-constexpr int kStages2 = 6;
+constexpr int kStages2 = 5;
 constexpr int kAStage2 = 128 * BK * 2;   // 16 KB: this CTA's 128 rows of A
 constexpr int kBStage2 = 128 * BK * 2;   // 16 KB: this CTA's 128 columns of B
-constexpr int kSmemBytes2 = kStages2 * (kAStage2 + kBStage2) + 1024 + 256;
+constexpr int kStgRow = 128 * 2 + 16;          // staged output row: 128 16-bit columns + 16 B pad (bank spread)
+constexpr int kStgWarp = 32 * kStgRow;         // per epilogue warp
+constexpr int kSmemBytes2 = kStages2 * (kAStage2 + kBStage2) + 1024 + 256 + 4 * kStgWarp;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -365,6 +367,62 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t adesc, uin
         "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
         : "memory");
+}
+
+// Epilogue of one warp's 32 rows x 256 columns for 16-bit outputs, staged through shared memory:
+// tcgen05.ld hands each thread one ROW (32 columns at a time); written straight to global memory
+// that is 32 different 128-byte lines per store instruction.  Instead the converted values go to a
+// per-warp buffer row by row and are read back so that half a warp covers 256 contiguous bytes of
+// one output row: every store instruction then writes two full 256-byte row segments.
+template <typename TO>
+__device__ __forceinline__ void epilogue_staged(const GemmArgs &g, uint32_t tmem_warp, int64_t row0, int64_t col_base,
+                                                uint8_t *stg, int lane) {
+    const int64_t row = row0 + lane;
+#pragma unroll 1
+    for (int h = 0; h < 2; ++h) {
+        const int64_t colh = col_base + h * 128;
+        if (colh >= g.N) break;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+            const int64_t col0 = colh + c * 32;
+            if (col0 >= g.N) break;
+            uint32_t r[32];
+            tmem_ld32(tmem_warp + h * 128 + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j0 = 0; j0 < 32; j0 += 8) {
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[j0 + j]);
+                if (col0 + j0 < g.N) {
+                    if (g.bias) {
+                        const float4 b0 = *reinterpret_cast<const float4 *>(g.bias + col0 + j0);
+                        const float4 b1 = *reinterpret_cast<const float4 *>(g.bias + col0 + j0 + 4);
+                        v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+                        v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+                    }
+                    if (g.accumulate && row < g.M) {
+                        const TO *crow = reinterpret_cast<const TO *>(g.c) + row * g.ldc + col0 + j0;
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) v[j] += Cvt<TO>::to_f(crow[j]);
+                    }
+                }
+                store8<TO>(reinterpret_cast<TO *>(stg + lane * kStgRow + (c * 32 + j0) * 2), v);
+            }
+        }
+        __syncwarp();
+        const int sub = lane >> 4, seg = lane & 15;          // two rows per pass, 16 x 16 bytes per row
+        const int64_t col = colh + seg * 8;
+#pragma unroll 4
+        for (int rr = 0; rr < 32; rr += 2) {
+            const int rl = rr + sub;
+            if (row0 + rl < g.M && col < g.N) {
+                const uint4 val = *reinterpret_cast<const uint4 *>(stg + rl * kStgRow + seg * 16);
+                *reinterpret_cast<uint4 *>(reinterpret_cast<TO *>(g.c) + (row0 + rl) * g.ldc + col) = val;
+            }
+        }
+        __syncwarp();
+    }
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -471,6 +529,7 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         // ------------------------------ epilogue (both CTAs, own rows) ------------------------------
         const int q = warp & 3;
         const uint32_t tempty_leader = map_to_cta(bar_tempty, 0);
+        uint8_t *stg = smem + kStages2 * (kAStage2 + kBStage2) + 256 + q * kStgWarp;
         int it = 0;
         for (int tile = pair; tile < ntiles; tile += npairs, ++it) {
             const int mb = tile / g.tiles_n, nb = tile % g.tiles_n;
@@ -478,19 +537,23 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             const uint32_t acc_phase = (it >> 1) & 1;
             if (!mbar_wait_bounded(bar_tfull + 8 * acc, acc_phase)) { if (lane == 0) atomicExch(g.err, 24); break; }
             tc_fence_after();
-            const int64_t row = (int64_t)mb * 256 + rank * 128 + q * 32 + lane;
+            const int64_t row0 = (int64_t)mb * 256 + rank * 128 + q * 32;
+            const int64_t row = row0 + lane;
             const int64_t col_base = (int64_t)nb * BN;
+            const uint32_t tmem_warp = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+            if (g.c_dtype == SRU_BF16) {
+                epilogue_staged<__nv_bfloat16>(g, tmem_warp, row0, col_base, stg, lane);
+            } else if (g.c_dtype == SRU_F16) {
+                epilogue_staged<__half>(g, tmem_warp, row0, col_base, stg, lane);
+            } else {
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                const int64_t col0 = col_base + c * 32;
-                if (col0 >= g.N) break;
-                uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, r);
-                tmem_ld_wait();
-                if (row < g.M) {
-                    if (g.c_dtype == SRU_BF16) epilogue_chunk<__nv_bfloat16>(g, r, row, col0);
-                    else if (g.c_dtype == SRU_F16) epilogue_chunk<__half>(g, r, row, col0);
-                    else epilogue_chunk<float>(g, r, row, col0);
+                for (int c = 0; c < BN / 32; ++c) {
+                    const int64_t col0 = col_base + c * 32;
+                    if (col0 >= g.N) break;
+                    uint32_t r[32];
+                    tmem_ld32(tmem_warp + c * 32, r);
+                    tmem_ld_wait();
+                    if (row < g.M) epilogue_chunk<float>(g, r, row, col0);
                 }
             }
             tc_fence_before();
