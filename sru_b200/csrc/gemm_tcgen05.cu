@@ -2,6 +2,10 @@
 //
 //   C[M,N] = op(A)[M,K] * op(B)[K,N] (+ col_bias[N]) (+ C),   fp32 accumulation in tensor memory.
 //
+// Two kernels share the pipeline below: a pair kernel (two SMs per 256x256 tile, cta_group::2,
+// described further down; used whenever there are enough tiles to fill the GPU) and the
+// single-CTA kernel described here (128x256 tiles; small problems).
+//
 // One persistent CTA per SM, 192 threads, warp-specialised:
 //   warp 0     TMA producer: cp.async.bulk.tensor loads of 128B-swizzled A / B tiles into a
 //              4-stage shared-memory ring, completion counted on "full" mbarriers;
