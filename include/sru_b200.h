@@ -180,6 +180,24 @@ int sru_b200_gemm(
     int64_t lda, int64_t ldb, int64_t ldc,
     int trans_a, int trans_b, int ab_dtype, int c_dtype, int accumulate, void *stream);
 
+/*
+ * The same contraction with caller-provided scratch.  Products whose output tiles alone
+ * cannot fill the GPU but whose reduction is long (the weight gradient x^T grad_U:
+ * M = input width, K = length * batch) are cut into K slabs whose fp32 partial results go to
+ * `workspace` and are summed by a second small kernel.  sru_b200_gemm_workspace_bytes()
+ * says how much scratch such a split wants (0: no split); with a NULL or smaller workspace
+ * the call behaves exactly like sru_b200_gemm.  Same library-GEMM counterpart in the
+ * reference as sru_b200_gemm (sru/modules.py:363-378 and its autograd).
+ */
+size_t sru_b200_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k_dim, int has_bias);
+
+int sru_b200_gemm_ws(
+    void *c, const void *a, const void *b, const float *col_bias,
+    int64_t m, int64_t n, int64_t k_dim,
+    int64_t lda, int64_t ldb, int64_t ldc,
+    int trans_a, int trans_b, int ab_dtype, int c_dtype, int accumulate,
+    void *workspace, size_t workspace_bytes, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -59,6 +59,7 @@ struct GemmArgs {
     int a_mn, b_mn;   // 1: MN-major operand
     uint32_t idesc;
     int tiles_m, tiles_n;
+    int ksplit, kbps;   // split-K: partial products over kbps k-blocks each go to slab sp of an fp32 workspace
     int *err;
 };
 
@@ -179,7 +180,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int ntiles = g.tiles_m * g.tiles_n;
+    const int nunits = g.tiles_m * g.tiles_n * g.ksplit;   // work units: (tile, k-split)
     const int nkb = (int)((g.K + BK - 1) / BK);
 
     if (threadIdx.x == 0) {
@@ -202,9 +203,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+            for (int unit = blockIdx.x; unit < nunits && ok; unit += gridDim.x) {
+                const int tile = unit / g.ksplit, sp = unit - tile * g.ksplit;
+                const int kb0 = sp * g.kbps, kb1 = min(nkb, kb0 + g.kbps);
                 const int mb = tile / g.tiles_n, nb = tile % g.tiles_n;
-                for (int kb = 0; kb < nkb; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1)) { atomicExch(g.err, 11); ok = false; break; }
                     const uint32_t full = bar_full + 8 * stage;
                     mbar_arrive_expect_tx(full, kAStage + kBStage);
@@ -239,13 +242,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             // two 8-row groups (2048 B) in an MN-major slab
             const uint32_t a_step = g.a_mn ? 2048u : 32u, b_step = g.b_mn ? 2048u : 32u;
             const uint32_t a_lbo = g.a_mn ? 8192u : 16u, b_lbo = g.b_mn ? 8192u : 16u;
-            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++it) {
+            for (int unit = blockIdx.x; unit < nunits && ok; unit += gridDim.x, ++it) {
+                const int tile = unit / g.ksplit, sp = unit - tile * g.ksplit;
+                const int kb0 = sp * g.kbps, kb1 = min(nkb, kb0 + g.kbps);
                 const int acc = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1;
                 if (!mbar_wait_bounded(bar_tempty + 8 * acc, acc_phase ^ 1)) { atomicExch(g.err, 12); break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < nkb; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait_bounded(bar_full + 8 * stage, phase)) { atomicExch(g.err, 13); ok = false; break; }
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem_a + stage * kAStage);
@@ -254,7 +259,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     for (int k16 = 0; k16 < BK / 16; ++k16) {
                         const uint64_t ad = make_desc(sa + k16 * a_step, a_lbo, 1024);
                         const uint64_t bd = make_desc(sb + k16 * b_step, b_lbo, 1024);
-                        tc_mma(d_tmem, ad, bd, g.idesc, (kb | k16) ? 1u : 0u);
+                        tc_mma(d_tmem, ad, bd, g.idesc, ((kb - kb0) | k16) ? 1u : 0u);
                     }
                     tc_commit(bar_empty + 8 * stage);   // stage reusable once these MMAs have read it
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -266,7 +271,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // --------------------------------- epilogue ---------------------------------
         const int q = warp & 3;  // TMEM lane quarter this warp may address
         int it = 0;
-        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++it) {
+        for (int unit = blockIdx.x; unit < nunits; unit += gridDim.x, ++it) {
+                const int tile = unit / g.ksplit, sp = unit - tile * g.ksplit;
+                const int kb0 = sp * g.kbps, kb1 = min(nkb, kb0 + g.kbps);
             const int mb = tile / g.tiles_n, nb = tile % g.tiles_n;
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
@@ -284,7 +291,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if (row < g.M) {
                     if (g.c_dtype == SRU_BF16) epilogue_chunk<__nv_bfloat16>(g, r, row, col0);
                     else if (g.c_dtype == SRU_F16) epilogue_chunk<__half>(g, r, row, col0);
-                    else epilogue_chunk<float>(g, r, row, col0);
+                    else epilogue_chunk<float>(g, r, row + (int64_t)sp * g.M, col0);
                 }
             }
             tc_fence_before();
@@ -446,7 +453,7 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();               // 0 = leader
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
-    const int ntiles = g.tiles_m * g.tiles_n;              // tiles of 256 x 256
+    const int nunits = g.tiles_m * g.tiles_n * g.ksplit;   // work units: (256 x 256 tile, k-split)
     const int nkb = (int)((g.K + BK - 1) / BK);
 
     if (threadIdx.x == 0) {
@@ -470,11 +477,13 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int tile = pair; tile < ntiles && ok; tile += npairs) {
+            for (int unit = pair; unit < nunits && ok; unit += npairs) {
+                const int tile = unit / g.ksplit, sp = unit - tile * g.ksplit;
+                const int kb0 = sp * g.kbps, kb1 = min(nkb, kb0 + g.kbps);
                 const int mb = tile / g.tiles_n, nb = tile % g.tiles_n;
                 const int m0 = mb * 256 + (int)rank * 128;      // this CTA's rows of A
                 const int n0 = nb * BN + (int)rank * 128;       // this CTA's columns of B
-                for (int kb = 0; kb < nkb; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1)) { atomicExch(g.err, 21); ok = false; break; }
                     const uint32_t full = bar_full + 8 * stage;
                     if (rank == 0) mbar_arrive_expect_tx(full, 2 * (kAStage2 + kBStage2));
@@ -506,13 +515,15 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             int it = 0;
             const uint32_t a_step = g.a_mn ? 2048u : 32u, b_step = g.b_mn ? 2048u : 32u;
             const uint32_t a_lbo = g.a_mn ? 8192u : 16u, b_lbo = g.b_mn ? 8192u : 16u;
-            for (int tile = pair; tile < ntiles && ok; tile += npairs, ++it) {
+            for (int unit = pair; unit < nunits && ok; unit += npairs, ++it) {
+                const int tile = unit / g.ksplit, sp = unit - tile * g.ksplit;
+                const int kb0 = sp * g.kbps, kb1 = min(nkb, kb0 + g.kbps);
                 const int acc = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1;
                 if (!mbar_wait_bounded(bar_tempty + 8 * acc, acc_phase ^ 1)) { atomicExch(g.err, 22); break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < nkb; ++kb) {
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait_bounded(bar_full + 8 * stage, phase)) { atomicExch(g.err, 23); ok = false; break; }
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem_a + stage * kAStage2);
@@ -521,7 +532,7 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                     for (int k16 = 0; k16 < BK / 16; ++k16) {
                         const uint64_t ad = make_desc(sa + k16 * a_step, a_lbo, 1024);
                         const uint64_t bd = make_desc(sb + k16 * b_step, b_lbo, 1024);
-                        tc_mma_pair(d_tmem, ad, bd, g.idesc, (kb | k16) ? 1u : 0u);
+                        tc_mma_pair(d_tmem, ad, bd, g.idesc, ((kb - kb0) | k16) ? 1u : 0u);
                     }
                     tc_commit_pair(bar_empty + 8 * stage);    // frees the stage in both CTAs
                     if (++stage == kStages2) { stage = 0; phase ^= 1; }
@@ -535,7 +546,9 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         const uint32_t tempty_leader = map_to_cta(bar_tempty, 0);
         uint8_t *stg = smem + kStages2 * (kAStage2 + kBStage2) + 256 + q * kStgWarp;
         int it = 0;
-        for (int tile = pair; tile < ntiles; tile += npairs, ++it) {
+        for (int unit = pair; unit < nunits; unit += npairs, ++it) {
+                const int tile = unit / g.ksplit, sp = unit - tile * g.ksplit;
+                const int kb0 = sp * g.kbps, kb1 = min(nkb, kb0 + g.kbps);
             const int mb = tile / g.tiles_n, nb = tile % g.tiles_n;
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
@@ -557,7 +570,7 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                     uint32_t r[32];
                     tmem_ld32(tmem_warp + c * 32, r);
                     tmem_ld_wait();
-                    if (row < g.M) epilogue_chunk<float>(g, r, row, col0);
+                    if (row < g.M) epilogue_chunk<float>(g, r, row + (int64_t)sp * g.M, col0);
                 }
             }
             tc_fence_before();
@@ -574,6 +587,46 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         tc_fence_after();
         tmem_dealloc2(tmem_base, kTmemCols);
     }
+}
+
+// Split-K tail: C = sum over slabs of the fp32 partial products (+ C when accumulating), converted.
+template <typename TO>
+__global__ void splitk_reduce(const float *__restrict__ ws, int nsplit, int64_t M, int64_t N, TO *__restrict__ c,
+                              int64_t ldc, int accumulate) {
+    const int64_t n4 = N / 4;   // N is a multiple of 8
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < M * n4; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = i / n4, col = (i - row * n4) * 4;
+        float4 acc = *reinterpret_cast<const float4 *>(ws + row * N + col);
+        for (int sp = 1; sp < nsplit; ++sp) {
+            const float4 v = *reinterpret_cast<const float4 *>(ws + ((int64_t)sp * M + row) * N + col);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        TO *o = c + row * ldc + col;
+        if (accumulate) {
+            acc.x += Cvt<TO>::to_f(o[0]); acc.y += Cvt<TO>::to_f(o[1]);
+            acc.z += Cvt<TO>::to_f(o[2]); acc.w += Cvt<TO>::to_f(o[3]);
+        }
+        o[0] = Cvt<TO>::from_f(acc.x); o[1] = Cvt<TO>::from_f(acc.y);
+        o[2] = Cvt<TO>::from_f(acc.z); o[3] = Cvt<TO>::from_f(acc.w);
+    }
+}
+
+// How many K slabs to cut a product into: only when the tiles alone leave the last wave of the
+// persistent grid badly filled and the reduction is long enough to amortise the extra pass.
+int choose_ksplit(int64_t tiles, int workers, int nkb) {
+    if (getenv("SRU_B200_GEMM_KSPLIT")) return std::max(1, std::min(atoi(getenv("SRU_B200_GEMM_KSPLIT")), 16));
+    // Measured on B200: once the tiles fill at least half of the GPU, splitting only costs L2 reuse
+    // between concurrently running tiles; it pays (up to 3x) when the grid would be mostly idle.
+    if (nkb < 64 || 2 * tiles > (int64_t)workers) return 1;
+    int best = 1;
+    double best_eff = 0.0;
+    for (int s = 1; s <= 8; ++s) {
+        if (nkb / s < 16) break;
+        const int64_t units = tiles * s;
+        const double eff = (double)units / (double)(((units + workers - 1) / workers) * workers);
+        if (eff > best_eff + 0.04) { best_eff = eff; best = s; }
+    }
+    return best;
 }
 
 // ---- host side --------------------------------------------------------------------------
@@ -613,9 +666,25 @@ int make_map(CUtensorMap *map, const void *base, int dtype, int64_t inner, int64
 
 using namespace srub;
 
-extern "C" int sru_b200_gemm(void *c, const void *a, const void *b, const float *col_bias, int64_t m, int64_t n,
-                             int64_t k_dim, int64_t lda, int64_t ldb, int64_t ldc, int trans_a, int trans_b,
-                             int ab_dtype, int c_dtype, int accumulate, void *stream) {
+// Kernel choice for a problem: pair kernel or single-CTA kernel, and the number of K slabs.
+static int gemm_plan(int64_t m, int64_t n, int64_t k_dim, bool has_bias, bool *two_sm, int *ksplit) {
+    int dev = 0, sms = 148;
+    SRUB_CUDA_CHECK(cudaGetDevice(&dev));
+    SRUB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const int64_t tiles256 = ((m + 255) / 256) * ((n + BN - 1) / BN);
+    bool pair = tiles256 >= sms / 2;
+    if (const char *e = getenv("SRU_B200_GEMM_2SM")) pair = (*e == '1');
+    const int64_t tiles = pair ? tiles256 : ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
+    const int nkb = (int)((k_dim + BK - 1) / BK);
+    *two_sm = pair;
+    *ksplit = has_bias ? 1 : choose_ksplit(tiles, pair ? sms / 2 : sms, nkb);
+    return 0;
+}
+
+static int gemm_impl(void *c, const void *a, const void *b, const float *col_bias, int64_t m, int64_t n,
+                     int64_t k_dim, int64_t lda, int64_t ldb, int64_t ldc, int trans_a, int trans_b,
+                     int ab_dtype, int c_dtype, int accumulate, void *workspace, size_t workspace_bytes,
+                     size_t *want_bytes, void *stream) {
     if (m < 0 || n < 0 || k_dim < 1) return set_error(SRU_ERR_BAD_ARG, "bad gemm sizes");
     if (m == 0 || n == 0) return 0;
     if (!c || !a || !b) return set_error(SRU_ERR_BAD_ARG, "gemm pointers must not be null");
@@ -636,13 +705,20 @@ extern "C" int sru_b200_gemm(void *c, const void *a, const void *b, const float 
     SRUB_CUDA_CHECK(cudaFree(nullptr));
 
     // Pair kernel (two SMs per 256 x 256 tile) once there are enough such tiles to fill the GPU;
-    // SRU_B200_GEMM_2SM=0/1 overrides.
+    // SRU_B200_GEMM_2SM=0/1 overrides.  Split-K needs a caller workspace; without one it is off.
     int dev = 0, sms = 148;
     SRUB_CUDA_CHECK(cudaGetDevice(&dev));
     SRUB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    const int64_t tiles256 = ((m + 255) / 256) * ((n + BN - 1) / BN);
-    bool two_sm = tiles256 >= sms / 2;
-    if (const char *e = getenv("SRU_B200_GEMM_2SM")) two_sm = (*e == '1');
+    bool two_sm = false;
+    int ksplit = 1;
+    if (int prc = gemm_plan(m, n, k_dim, col_bias != nullptr, &two_sm, &ksplit)) return prc;
+    const int nkb_all = (int)((k_dim + BK - 1) / BK);
+    int kbps = (nkb_all + ksplit - 1) / ksplit;
+    ksplit = (nkb_all + kbps - 1) / kbps;
+    if (ksplit > 1 && (!workspace || workspace_bytes < (size_t)ksplit * m * n * sizeof(float))) {
+        ksplit = 1;
+        kbps = nkb_all;
+    }
 
     CUtensorMap map_a, map_b;
     int rc;
@@ -672,7 +748,14 @@ extern "C" int sru_b200_gemm(void *c, const void *a, const void *b, const float 
     g.tiles_n = (int)((n + BN - 1) / BN);
     g.err = device_error_flag();
     if (!g.err) return set_error(SRU_ERR_CUDA, "device error flag unavailable");
-    const int64_t ntiles = (int64_t)g.tiles_m * g.tiles_n;
+    g.ksplit = ksplit;
+    g.kbps = kbps;
+    void *final_c = c;
+    const int final_dtype = c_dtype, final_acc = g.accumulate;
+    if (ksplit > 1) {   // partial products go to [ksplit][M][N] fp32; splitk_reduce finishes the job
+        g.c = workspace; g.ldc = n; g.c_dtype = SRU_F32; g.accumulate = 0;
+    }
+    const int64_t ntiles = (int64_t)g.tiles_m * g.tiles_n * ksplit;   // work units
     if (ntiles > 0x7fffffff) return set_error(SRU_ERR_BAD_ARG, "too many gemm tiles");
 
     static bool attr_set[64] = {false};
@@ -701,5 +784,41 @@ extern "C" int sru_b200_gemm(void *c, const void *a, const void *b, const float 
         gemm_tcgen05_kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(map_a, map_b, g);
     }
     SRUB_CUDA_CHECK(cudaGetLastError());
+    if (ksplit > 1) {
+        const int64_t items = m * (n / 4);
+        const unsigned blocks = (unsigned)std::min<int64_t>((items + 255) / 256, (int64_t)sms * 8);
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        const float *ws = static_cast<const float *>(workspace);
+        if (final_dtype == SRU_BF16)
+            splitk_reduce<__nv_bfloat16><<<blocks, 256, 0, st>>>(ws, ksplit, m, n, (__nv_bfloat16 *)final_c, ldc, final_acc);
+        else if (final_dtype == SRU_F16)
+            splitk_reduce<__half><<<blocks, 256, 0, st>>>(ws, ksplit, m, n, (__half *)final_c, ldc, final_acc);
+        else
+            splitk_reduce<float><<<blocks, 256, 0, st>>>(ws, ksplit, m, n, (float *)final_c, ldc, final_acc);
+        SRUB_CUDA_CHECK(cudaGetLastError());
+    }
     return 0;
+}
+
+extern "C" int sru_b200_gemm(void *c, const void *a, const void *b, const float *col_bias, int64_t m, int64_t n,
+                             int64_t k_dim, int64_t lda, int64_t ldb, int64_t ldc, int trans_a, int trans_b,
+                             int ab_dtype, int c_dtype, int accumulate, void *stream) {
+    return gemm_impl(c, a, b, col_bias, m, n, k_dim, lda, ldb, ldc, trans_a, trans_b, ab_dtype, c_dtype, accumulate,
+                     nullptr, 0, nullptr, stream);
+}
+
+extern "C" size_t sru_b200_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k_dim, int has_bias) {
+    if (m <= 0 || n <= 0 || k_dim <= 0) return 0;
+    bool two_sm = false;
+    int ksplit = 1;
+    if (gemm_plan(m, n, k_dim, has_bias != 0, &two_sm, &ksplit) != 0 || ksplit <= 1) return 0;
+    return (size_t)ksplit * (size_t)m * (size_t)n * sizeof(float);
+}
+
+extern "C" int sru_b200_gemm_ws(void *c, const void *a, const void *b, const float *col_bias, int64_t m, int64_t n,
+                                int64_t k_dim, int64_t lda, int64_t ldb, int64_t ldc, int trans_a, int trans_b,
+                                int ab_dtype, int c_dtype, int accumulate, void *workspace, size_t workspace_bytes,
+                                void *stream) {
+    return gemm_impl(c, a, b, col_bias, m, n, k_dim, lda, ldb, ldc, trans_a, trans_b, ab_dtype, c_dtype, accumulate,
+                     workspace, workspace_bytes, nullptr, stream);
 }

@@ -53,15 +53,19 @@ def gemm(a: Tensor, b: Tensor, trans_a: bool = False, trans_b: bool = False,
     if kd == 0:
         return out if accumulate else out.zero_()
     bias = None if col_bias is None else col_bias.detach().float().contiguous()
+    L = _lib.lib()
     with torch.cuda.device(a.device):
         if name is None:
             name = "gemm_wgrad" if trans_a else ("gemm_dgrad" if trans_b else "gemm_fwd")
+        # long reductions into few output tiles are cut into K slabs; the library says how much scratch it wants
+        ws_bytes = int(L.sru_b200_gemm_workspace_bytes(m, n, kd, 0 if bias is None else 1))
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device) if ws_bytes else None
         _lib.call(
-            name, 1, _lib.lib().sru_b200_gemm,
+            name, 2 if ws_bytes else 1, L.sru_b200_gemm_ws,
             _lib.ptr(out), _lib.ptr(a), _lib.ptr(b), _lib.ptr(bias), m, n, kd,
             a.stride(0), b.stride(0), out.stride(0), int(trans_a), int(trans_b),
             _lib.DTYPE_CODE[a.dtype], _lib.DTYPE_CODE[out.dtype], int(accumulate),
-            _lib.current_stream_ptr(a.device))
+            _lib.ptr(ws), ws_bytes, _lib.current_stream_ptr(a.device))
     return out
 
 
