@@ -94,5 +94,41 @@ __host__ __device__ __forceinline__ uint32_t align128(uint32_t v) { return (v + 
 
 template <bool B> using BoolC = std::integral_constant<bool, B>;
 
+// Reads a Pack from shared memory with explicit shared-space loads.  A read through a generic pointer is
+// tracked like a global load (long scoreboard) and may not be moved across the global stores of the step
+// before it; ld.shared is neither, which is what lets a lone warp overlap one step's reads with the
+// previous step's dependent chain.  The asm is not volatile, so that the compiler too may move it over
+// stores; what keeps it behind the mbarrier wait that guards the data is its address: the caller passes
+// the stage base through order_after_wait() right after the wait.
+__device__ __forceinline__ uint32_t order_after_wait(uint32_t addr) {
+    asm volatile("" : "+r"(addr) : : "memory");
+    return addr;
+}
+template <typename P> __device__ __forceinline__ P lds_pack(uint32_t addr) {
+    constexpr int A = alignof(P), NB = sizeof(P);
+    P out;
+    if constexpr (A == 16) {
+        uint4 *o = reinterpret_cast<uint4 *>(&out);
+#pragma unroll
+        for (int i = 0; i < NB / 16; ++i)
+            asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(o[i].x), "=r"(o[i].y), "=r"(o[i].z), "=r"(o[i].w) : "r"(addr + 16 * i));
+    } else if constexpr (A == 8) {
+        uint2 *o = reinterpret_cast<uint2 *>(&out);
+#pragma unroll
+        for (int i = 0; i < NB / 8; ++i)
+            asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(o[i].x), "=r"(o[i].y) : "r"(addr + 8 * i));
+    } else if constexpr (A == 4) {
+        uint32_t *o = reinterpret_cast<uint32_t *>(&out);
+#pragma unroll
+        for (int i = 0; i < NB / 4; ++i) asm("ld.shared.u32 %0, [%1];" : "=r"(o[i]) : "r"(addr + 4 * i));
+    } else {
+        uint16_t *o = reinterpret_cast<uint16_t *>(&out);
+#pragma unroll
+        for (int i = 0; i < NB / 2; ++i) asm("ld.shared.u16 %0, [%1];" : "=h"(o[i]) : "r"(addr + 2 * i));
+    }
+    return out;
+}
+
 
 }  // namespace srub

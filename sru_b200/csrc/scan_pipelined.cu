@@ -158,16 +158,16 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const __grid_constant__ Sca
 
     // One block of kTS steps.  ub / xb point at this thread's slice in the block's first time slab;
     // dsu / dsx step to the next slab in scan order (negative for descending tiles).
-    auto block = [&](const uint8_t *ub, const uint8_t *xb, int dsu, int dsx, uint32_t pad_bits, int steps,
+    auto block = [&](uint32_t ub, uint32_t xb, int dsu, int dsx, uint32_t pad_bits, int steps,
                      auto pad_c, auto hist_c, auto full_c) {
         constexpr bool PAD = decltype(pad_c)::value, HIST = decltype(hist_c)::value, FULL = decltype(full_c)::value;
 #pragma unroll
         for (int ts = 0; ts < kTS; ++ts) {
             if (!FULL && ts >= steps) break;
             const bool pad = PAD && ((pad_bits >> ts) & 1u);
-            const Pack<T, V * K> up = *reinterpret_cast<const Pack<T, V * K> *>(ub + ts * dsu);
+            const Pack<T, V * K> up = lds_pack<Pack<T, V * K>>(ub + ts * dsu);
             Pack<T, V> xp;
-            if (has_x) xp = *reinterpret_cast<const Pack<T, V> *>(xb + ts * dsx);
+            if (has_x) xp = lds_pack<Pack<T, V>>(xb + ts * dsx);
             float hv[V];
 #pragma unroll
             for (int i = 0; i < V; ++i) {
@@ -205,15 +205,15 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const __grid_constant__ Sca
                 atomicExch(p.err, 2);
                 break;
             }
-            const uint8_t *sb = stage0 + (size_t)s * stage_bytes;
+            const uint32_t sb = order_after_wait(smem_u32(stage0) + (uint32_t)s * stage_bytes);
             for (int q = 0; q < SS && n < L; q += kTS, n += kTS) {
                 const uint32_t pad_cur = pad0;
                 pad0 = pad1;
                 pad1 = load_pad(n + 2 * kTS);
                 if (active && !(p.c.debug & 2)) {
                     const int slab = asc ? q : (SS - 1 - q);
-                    const uint8_t *ub = sb + u_off + slab * su;
-                    const uint8_t *xb = sb + x_off + slab * sx;
+                    const uint32_t ub = sb + u_off + slab * su;
+                    const uint32_t xb = sb + x_off + slab * sx;
                     const int64_t left = L - n;
                     if (left >= kTS) block(ub, xb, asc ? su : -su, asc ? sx : -sx, pad_cur, kTS, pad_c, hist_c, BoolC<true>{});
                     else block(ub, xb, asc ? su : -su, asc ? sx : -sx, pad_cur, (int)left, pad_c, hist_c, BoolC<false>{});
@@ -366,7 +366,7 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const __grid_constant__ Sca
 
         // One block of kTS steps.  LAST marks the final block (ragged, and holding the step whose
         // predecessor state is c_init); all other blocks are full and branch-free.
-        auto block = [&](const uint8_t *sb, int slab, int dslab, uint32_t pad_bits, int steps, auto pad_c, auto last_c) {
+        auto block = [&](uint32_t sb, int slab, int dslab, uint32_t pad_bits, int steps, auto pad_c, auto last_c) {
             constexpr bool PAD = decltype(pad_c)::value, LAST = decltype(last_c)::value;
 #pragma unroll
             for (int ts = 0; ts < kTS; ++ts) {
@@ -374,11 +374,11 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const __grid_constant__ Sca
                 const bool pad = PAD && ((pad_bits >> ts) & 1u);
                 const bool at_start = LAST && (ts == steps - 1);
                 const int sl = slab + ts * dslab;
-                const Pack<T, V * K> up = *reinterpret_cast<const Pack<T, V * K> *>(sb + u_off + sl * su);
-                const Pack<T, V> ghp = *reinterpret_cast<const Pack<T, V> *>(sb + g_off + sl * sg);
+                const Pack<T, V * K> up = lds_pack<Pack<T, V * K>>(sb + u_off + sl * su);
+                const Pack<T, V> ghp = lds_pack<Pack<T, V>>(sb + g_off + sl * sg);
                 Pack<T, V> xp;
-                if (has_x) xp = *reinterpret_cast<const Pack<T, V> *>(sb + x_off + sl * sx);
-                const Pack<TC, V> cpp = *reinterpret_cast<const Pack<TC, V> *>(sb + c_off + sl * sc);
+                if (has_x) xp = lds_pack<Pack<T, V>>(sb + x_off + sl * sx);
+                const Pack<TC, V> cpp = lds_pack<Pack<TC, V>>(sb + c_off + sl * sc);
                 float guv[V * K], gxv_[V];
 #pragma unroll
                 for (int i = 0; i < V; ++i) {
@@ -436,7 +436,7 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const __grid_constant__ Sca
                     atomicExch(p.err, 4);
                     break;
                 }
-                const uint8_t *sb = stage0 + (size_t)s * stage_bytes;
+                const uint32_t sb = order_after_wait(smem_u32(stage0) + (uint32_t)s * stage_bytes);
                 for (int q = 0; q < SS && m < L; q += kTS, m += kTS) {
                     const uint32_t pad_cur = pad0;
                     pad0 = pad1;
@@ -545,15 +545,19 @@ static bool choose_tile(int64_t L, int64_t B, int64_t d, int dirs, int k, int sk
     if (d % granule != 0 || L < 1 || B < 1 || L > 0x7fffff00 || B > 0x7fffffff) return false;
     const int64_t D = d * dirs, ncols = B * D;
     const int sms = num_sms();
-    const int vmax = 4, vmin = 2;
+    const int vmax = 4, vmin = 1;
     // Columns per thread, from sweeps on B200: V = 4 amortises the per-step overhead best once it
     // still leaves eight or more warps per SM; below that the scan is bound by per-step latency
-    // and V = 2 (twice the warps) wins.  V = 1 and V = 8 never did.
+    // and V = 2 (twice the warps) wins.  With fewer than four warps of columns per SM the forward
+    // does best with V = 1 (a lone warp issues one column's step in less time than two); the backward,
+    // with twice the reads per step, never did, and V = 8 never did anywhere.
     int v = (ncols / (32 * 4) >= (int64_t)sms * 8) ? 4 : 2;
+    if (!backward && ncols / 128 < (int64_t)sms * 4) v = 1;
     v = env_int(backward ? "SRU_B200_BWD_V" : "SRU_B200_FWD_V", v);
     if (v < vmin || v > vmax || (v & (v - 1))) return false;
     // consumer threads per CTA: two warps, one when that is needed to give every SM a CTA
     int ntc = (ncols / ((int64_t)v * 64) >= (int64_t)sms) ? 64 : 32;
+    if (v == 1 && ncols / 128 >= (int64_t)sms * 3 / 4) ntc = 128;   // one CTA of four warps per SM
     ntc = env_int("SRU_B200_SCAN_THREADS", ntc);
     if (ntc < 32 || ntc > 128 || ntc % 32) return false;
     // hidden width of the tile: largest divisor of d, multiple of the granule, <= v*ntc, and with a
@@ -641,6 +645,7 @@ static int launch_t(const ScanMaps &maps, const PipeArgs &p, bool backward, cuda
 template <typename T, typename TC, int K>
 static int launch_v(const ScanMaps &maps, const PipeArgs &p, bool backward, cudaStream_t st) {
     switch (p.c.v) {
+        case 1: return launch_t<T, TC, 1, K>(maps, p, backward, st);
         case 2: return launch_t<T, TC, 2, K>(maps, p, backward, st);
         case 4: return launch_t<T, TC, 4, K>(maps, p, backward, st);
     }

@@ -113,3 +113,27 @@ def test_projection_autograd_matches_library():
         assert rel_err(u, ur) <= 1e-2 and rel_err(x.grad, xr.grad) <= 1e-2 and rel_err(w.grad, wr.grad) <= 1e-2
     finally:
         os.environ.pop("SRU_B200_GEMM", None)
+
+
+@pytest.mark.parametrize("force", [None, "4"])
+def test_gemm_split_k(force):
+    """Weight-gradient shape that under-fills the GPU (narrow input layer, long reduction): the K slabs'
+    fp32 partials plus the reduction kernel must give the same product; also with accumulation."""
+    import os
+    gemm = _gemm()
+    g = torch.Generator().manual_seed(21)
+    M, N, K = 120, 1024, 8192
+    a = (torch.randn(K, M, generator=g) * 0.1).bfloat16().to(DEV)
+    b = (torch.randn(K, N, generator=g) * 0.1).bfloat16().to(DEV)
+    ref = a.float().t() @ b.float()
+    if force:
+        os.environ["SRU_B200_GEMM_KSPLIT"] = force
+    try:
+        out = gemm(a, b, trans_a=True, out_dtype=torch.float32)
+        out16 = gemm(a, b, trans_a=True)
+        base = torch.randn(M, N, generator=g).to(DEV)
+        acc = base.clone()
+        gemm(a, b, trans_a=True, out=acc, accumulate=True)
+    finally:
+        os.environ.pop("SRU_B200_GEMM_KSPLIT", None)
+    assert rel_err(out, ref) <= 1e-4 and rel_err(out16, ref) <= 1e-2 and rel_err(acc, ref + base) <= 1e-4
