@@ -49,6 +49,22 @@ template <int MODE> struct Gate {
             return fmaf(tanh_approx(fmaf(c, wcf, fmaf(u, 0.5f, bf))), 0.5f, 0.5f);
         }
     }
+    // The gate and its complement 1 - g for the backward pass.  fp32 storage: both with full relative
+    // accuracy (1 - g from the rounded g loses the digits g shares with 1; gradients are multiplied by it):
+    // with a = exp(-|z|), r = 1/(1+a), the larger of the two is r and the smaller a*r.
+    static __device__ __forceinline__ float eval_pair(float c, float wcf, float u, float bf, float *one_minus) {
+        if (MODE == 0) {
+            const float z = fmaf(wcf, c, u) + bf;
+            const float a = expf(-fabsf(z));
+            const float r = 1.f / (1.f + a), q = a * r;
+            *one_minus = (z >= 0.f) ? q : r;
+            return (z >= 0.f) ? r : q;
+        } else {
+            *one_minus = 0.f;   // not used: see kPair
+            return eval(c, wcf, u, bf);
+        }
+    }
+    static constexpr bool kPair = (MODE == 0);   // eval_pair delivers the complement
 };
 template <typename T> using GateFor = Gate<sizeof(T) == 4 ? 0 : 2>;
 
@@ -128,6 +144,56 @@ template <typename P> __device__ __forceinline__ P lds_pack(uint32_t addr) {
         for (int i = 0; i < NB / 2; ++i) asm("ld.shared.u16 %0, [%1];" : "=h"(o[i]) : "r"(addr + 2 * i));
     }
     return out;
+}
+
+// ---------------------------------------------------------------------------------------
+// Pad flags.  mask_pad is (L, B) bytes; a consumer needs one flag per step of its row.  Read from
+// global memory by the consumer itself, each flag's latency lands in a warp that has nothing else to
+// run while it waits, which halves the throughput of small problems.  Instead the 32 lanes of the
+// producer warp read the flags of a whole stage (rows x steps) one stage ahead, keep them in
+// registers across the wait for the stage to drain, and write them into the stage as [row][step]
+// bytes before the stage's full barrier is armed; consumers then take four steps' flags with one
+// shared-memory word.
+// ---------------------------------------------------------------------------------------
+constexpr int kPadPerLane = 8;                 // flags per lane and stage: rows x steps <= 256
+struct PadStager {
+    const uint8_t *mask;
+    int64_t B, L, b0;
+    int nflags, ss, lane;
+    uint32_t v[kPadPerLane];
+    __device__ __forceinline__ PadStager(const uint8_t *mask_, int64_t B_, int64_t L_, int64_t b0_, int br, int ss_, int lane_)
+        : mask(mask_), B(B_), L(L_), b0(b0_), nflags(br * ss_), ss(ss_), lane(lane_) {}
+    // requests the flags of the stage whose first time step is t0 (steps outside [0, L) and rows
+    // past the batch read as 0)
+    __device__ __forceinline__ void fetch(int t0) {
+#pragma unroll
+        for (int j = 0; j < kPadPerLane; ++j) {
+            const int e = lane + 32 * j;
+            const int rr = e / ss, st = e - rr * ss;
+            const int64_t t = (int64_t)t0 + st;
+            v[j] = 0;
+            if (e < nflags && t >= 0 && t < L && b0 + rr < B) v[j] = mask[t * B + b0 + rr];
+        }
+    }
+    __device__ __forceinline__ void store(uint32_t dst) const {
+#pragma unroll
+        for (int j = 0; j < kPadPerLane; ++j) {
+            const int e = lane + 32 * j;
+            if (e < nflags) {
+                const uint16_t f = (uint16_t)(v[j] ? 1 : 0);
+                asm volatile("st.shared.u8 [%0], %1;" : : "r"(dst + e), "h"(f) : "memory");
+            }
+        }
+    }
+};
+
+// Flags of the four steps of the block that starts q steps into the stage: byte ts belongs to scan
+// step ts.  row_flags is the shared address of this row's ss flags, stored in time order; a
+// descending tile walks them from the end, so its word is byte-reversed.
+__device__ __forceinline__ uint32_t pad_word(uint32_t row_flags, int q, int ss, bool asc) {
+    uint32_t w;
+    asm("ld.shared.u32 %0, [%1];" : "=r"(w) : "r"(row_flags + (asc ? q : ss - kTS - q)));
+    return asc ? w : __byte_perm(w, 0, 0x0123);
 }
 
 

@@ -68,12 +68,14 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const __grid_constant__ Sca
     const uint32_t x_slab = has_x ? (uint32_t)HW * sizeof(T) : 0;
     const uint32_t u_region = align128(SS * BR * u_slab);
     const uint32_t x_region = align128(SS * BR * x_slab);
-    const uint32_t stage_bytes = u_region + x_region;
+    const bool has_pad = a.mask_pad != nullptr;
+    const uint32_t pad_region = has_pad ? align128(SS * BR) : 0;   // flags [row][step of the stage], one byte each
+    const uint32_t stage_bytes = u_region + x_region + pad_region;
     uint8_t *stage0 = smem + kBarBytes;
 
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
-            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_full + 8 * s, a.mask_pad ? 2 : 1);   // the copies' arrive, and the pad flags'
             mbar_init(bar_empty + 8 * s, nthr_c / 32);
         }
         fence_mbar_init();
@@ -81,24 +83,38 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const __grid_constant__ Sca
     __syncthreads();
 
     if (tid >= nthr_c) {
-        // ------------------------------ producer (one thread) ------------------------------
-        if (lane != 0) return;
+        // ------------------- producer warp: lane 0 issues the copies, all lanes stage the pad flags -------------------
         const int xu = (int)(dj0 * K * sizeof(T) / 8), xx = (int)(dj0 * sizeof(T) / 8);
+        PadStager pads(a.mask_pad, a.B, L, b0, BR, SS, lane);
+        // ascending tiles take times [it*SS, it*SS+SS); descending ones the mirrored window,
+        // which may start below 0 (the box is zero-filled there, the flags read as "not padded")
+        auto first_time = [&](int it) { return asc ? it * SS : (int)(L - (int64_t)(it + 1) * SS); };
+        if (has_pad) pads.fetch(first_time(0));
         int s = 0;
         uint32_t ph = 1;   // the first pass over the ring finds every stage free
         for (int it = 0; it < nst; ++it) {
-            if (!mbar_wait_bounded(bar_empty + 8 * s, ph)) { atomicExch(p.err, 1); break; }
+            int ok = (lane == 0) ? (int)mbar_wait_bounded(bar_empty + 8 * s, ph) : 1;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) { if (lane == 0) atomicExch(p.err, 1); break; }
             const uint32_t bar = bar_full + 8 * s;
-            if (p.c.debug & 1) {
-                mbar_arrive(bar);
-            } else {
-                // ascending tiles take times [it*SS, it*SS+SS); descending ones the mirrored window,
-                // which may start below 0 (the box is zero-filled there)
-                const int t0 = asc ? it * SS : (int)(L - (int64_t)(it + 1) * SS);
-                mbar_arrive_expect_tx(bar, (uint32_t)SS * BR * (u_slab + x_slab));
-                const uint32_t sbase = smem_u32(stage0) + (uint32_t)s * stage_bytes;
-                tma_load_3d(sbase, &maps.u, bar, xu, (int)b0, t0);
-                if (has_x) tma_load_3d(sbase + u_region, &maps.x, bar, xx, (int)b0, t0);
+            const uint32_t sbase = smem_u32(stage0) + (uint32_t)s * stage_bytes;
+            if (lane == 0) {
+                if (p.c.debug & 1) {
+                    mbar_arrive(bar);
+                } else {
+                    const int t0 = first_time(it);
+                    mbar_arrive_expect_tx(bar, (uint32_t)SS * BR * (u_slab + x_slab));
+                    tma_load_3d(sbase, &maps.u, bar, xu, (int)b0, t0);
+                    if (has_x) tma_load_3d(sbase + u_region, &maps.x, bar, xx, (int)b0, t0);
+                }
+            }
+            if (has_pad) {
+                // this stage's flags were read from global memory one stage ago; the next stage's are
+                // requested now and not looked at until the next trip, so their latency stays off every path
+                pads.store(sbase + u_region + x_region);
+                if (it + 1 < nst) pads.fetch(first_time(it + 1));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar);   // second arrival: releases all lanes' flag writes to the consumers
             }
             if (++s == NS) { s = 0; ph ^= 1; }
         }
@@ -111,7 +127,6 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const __grid_constant__ Sca
     const bool active = (tid < BR * TPR) && (r < nrows);
     const int64_t b = b0 + (active ? r : 0);
     const int64_t col = b * D + dj0 + hc;
-    const bool has_pad = a.mask_pad != nullptr;
     const bool has_hist = a.c_hist != nullptr;
 
     float c[V], wc1n[V], wc2n[V], b1n[V], b2n[V], mk[V];
@@ -138,23 +153,10 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const __grid_constant__ Sca
     const int64_t ostep = asc ? (a.B * D) : -(a.B * D);
     T *hp = (T *)a.h + (t_first * a.B + b) * D + dj0 + hc;
     TC *cp = (TC *)a.c_hist + (has_hist ? (t_first * a.B + b) * D + dj0 + hc : 0);
-    const int64_t pstep = asc ? a.B : -a.B;
-    const uint8_t *pp = has_pad ? a.mask_pad + t_first * a.B + b : nullptr;
     const int su = BR * (int)u_slab, sx = BR * (int)x_slab;      // bytes between time slabs of a stage
     const uint32_t u_off = r * u_slab + hc * K * sizeof(T);
     const uint32_t x_off = u_region + r * x_slab + hc * sizeof(T);
-
-    // pad flags of scan steps n_first .. n_first+3, one bit each; fetched two blocks ahead
-    auto load_pad = [&](int64_t n_first) -> uint32_t {
-        uint32_t bits = 0;
-        if (has_pad && active) {
-            const uint8_t *q = pp + n_first * pstep;
-#pragma unroll
-            for (int ts = 0; ts < kTS; ++ts)
-                if (n_first + ts < L) bits |= (q[ts * pstep] ? 1u : 0u) << ts;
-        }
-        return bits;
-    };
+    const uint32_t pad_off = u_region + x_region + r * SS;       // this row's flags of the stage
 
     // One block of kTS steps.  ub / xb point at this thread's slice in the block's first time slab;
     // dsu / dsx step to the next slab in scan order (negative for descending tiles).
@@ -164,7 +166,7 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const __grid_constant__ Sca
 #pragma unroll
         for (int ts = 0; ts < kTS; ++ts) {
             if (!FULL && ts >= steps) break;
-            const bool pad = PAD && ((pad_bits >> ts) & 1u);
+            const bool pad = PAD && ((pad_bits >> (8 * ts)) & 0xffu);
             const Pack<T, V * K> up = lds_pack<Pack<T, V * K>>(ub + ts * dsu);
             Pack<T, V> xp;
             if (has_x) xp = lds_pack<Pack<T, V>>(xb + ts * dsx);
@@ -196,7 +198,7 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const __grid_constant__ Sca
     };
 
     auto run = [&](auto pad_c, auto hist_c) {
-        uint32_t pad0 = load_pad(0), pad1 = load_pad(kTS);
+        constexpr bool PADF = decltype(pad_c)::value;
         int s = 0;
         uint32_t ph = 0;
         int64_t n = 0;   // scan step of the next block
@@ -207,11 +209,10 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const __grid_constant__ Sca
             }
             const uint32_t sb = order_after_wait(smem_u32(stage0) + (uint32_t)s * stage_bytes);
             for (int q = 0; q < SS && n < L; q += kTS, n += kTS) {
-                const uint32_t pad_cur = pad0;
-                pad0 = pad1;
-                pad1 = load_pad(n + 2 * kTS);
                 if (active && !(p.c.debug & 2)) {
                     const int slab = asc ? q : (SS - 1 - q);
+                    // the block's four flags, byte ts = scan step ts of the block
+                    const uint32_t pad_cur = PADF ? pad_word(sb + pad_off, q, SS, asc) : 0u;
                     const uint32_t ub = sb + u_off + slab * su;
                     const uint32_t xb = sb + x_off + slab * sx;
                     const int64_t left = L - n;
@@ -273,12 +274,15 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const __grid_constant__ Sca
     const uint32_t x_region = align128(SS * BR * x_slab);
     const uint32_t c_region = align128(SS * BR * c_slab);
     const uint32_t g_region = align128(SS * BR * g_slab);
-    const uint32_t stage_bytes = u_region + x_region + c_region + g_region;
+    const bool has_pad = a.mask_pad != nullptr;
+    const uint32_t pad_region = has_pad ? align128(SS * BR) : 0;   // flags [row][step of the stage], one byte each
+    const uint32_t in_region = u_region + x_region + c_region + g_region;
+    const uint32_t stage_bytes = in_region + pad_region;
     uint8_t *stage0 = smem + kBarBytes;
 
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
-            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_full + 8 * s, a.mask_pad ? 2 : 1);   // the copies' arrive, and the pad flags'
             mbar_init(bar_empty + 8 * s, nthr_c / 32);
         }
         fence_mbar_init();
@@ -293,32 +297,42 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const __grid_constant__ Sca
     for (int i = 0; i < V; ++i) { gwc1[i] = 0.f; gwc2[i] = 0.f; gb1[i] = 0.f; gb2[i] = 0.f; }
 
     if (tid >= nthr_c) {
-        // ------------------------------ producer (one thread) ------------------------------
-        if (lane == 0) {
-            const int xu = (int)(dj0 * K * sizeof(T) / 8), xx = (int)(dj0 * sizeof(T) / 8);
-            const int xc = (int)(dj0 * sizeof(TC) / 8);
-            int s = 0;
-            uint32_t ph = 1;
-            for (int it = 0; it < nst; ++it) {
-                if (!mbar_wait_bounded(bar_empty + 8 * s, ph)) { atomicExch(p.err, 3); break; }
-                const uint32_t bar = bar_full + 8 * s;
-                const int t0 = asc ? it * SS : (int)(L - (int64_t)(it + 1) * SS);
+        // ------------------- producer warp: lane 0 issues the copies, all lanes stage the pad flags -------------------
+        const int xu = (int)(dj0 * K * sizeof(T) / 8), xx = (int)(dj0 * sizeof(T) / 8);
+        const int xc = (int)(dj0 * sizeof(TC) / 8);
+        PadStager pads(a.mask_pad, a.B, L, b0, BR, SS, lane);
+        auto first_time = [&](int it) { return asc ? it * SS : (int)(L - (int64_t)(it + 1) * SS); };
+        if (has_pad) pads.fetch(first_time(0));
+        int s = 0;
+        uint32_t ph = 1;
+        for (int it = 0; it < nst; ++it) {
+            int ok = (lane == 0) ? (int)mbar_wait_bounded(bar_empty + 8 * s, ph) : 1;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) { if (lane == 0) atomicExch(p.err, 3); break; }
+            const uint32_t bar = bar_full + 8 * s;
+            const uint32_t sbase = smem_u32(stage0) + (uint32_t)s * stage_bytes;
+            if (lane == 0) {
+                const int t0 = first_time(it);
                 mbar_arrive_expect_tx(bar, (uint32_t)SS * BR * (u_slab + x_slab + c_slab + g_slab));
-                const uint32_t sbase = smem_u32(stage0) + (uint32_t)s * stage_bytes;
                 tma_load_3d(sbase, &maps.u, bar, xu, (int)b0, t0);
                 if (has_x) tma_load_3d(sbase + u_region, &maps.x, bar, xx, (int)b0, t0);
                 // the state BEFORE each step: one time step further along this walk (out-of-range rows,
                 // i.e. the predecessor of the sequence start, are zero-filled and replaced by c_init)
                 tma_load_3d(sbase + u_region + x_region, &maps.c, bar, xc, (int)b0, asc ? t0 + 1 : t0 - 1);
                 tma_load_3d(sbase + u_region + x_region + c_region, &maps.g, bar, xx, (int)b0, t0);
-                if (++s == NS) { s = 0; ph ^= 1; }
             }
+            if (has_pad) {
+                pads.store(sbase + in_region);
+                if (it + 1 < nst) pads.fetch(first_time(it + 1));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar);   // second arrival: releases all lanes' flag writes to the consumers
+            }
+            if (++s == NS) { s = 0; ph ^= 1; }
         }
     } else {
         // -------------------------------- consumers --------------------------------
         const int64_t b = b0 + (active ? r : 0);
         const int64_t col = b * D + dj0 + hc;
-        const bool has_pad = a.mask_pad != nullptr;
         float cur[V], wc1n[V], wc2n[V], b1n[V], b2n[V], mk[V], c0[V];
 #pragma unroll
         for (int i = 0; i < V; ++i) {
@@ -345,24 +359,12 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const __grid_constant__ Sca
         const int64_t o_first = (t_first * a.B + b) * D + dj0 + hc;
         T *gup = (T *)a.grad_u + o_first * K;
         T *gxp = (T *)a.grad_x + (has_x ? o_first : 0);
-        const int64_t pstep = asc ? a.B : -a.B;
-        const uint8_t *pp = has_pad ? a.mask_pad + t_first * a.B + b : nullptr;
         const int su = BR * (int)u_slab, sx = BR * (int)x_slab, sc = BR * (int)c_slab, sg = BR * (int)g_slab;
         const uint32_t u_off = r * u_slab + hc * K * sizeof(T);
         const uint32_t x_off = u_region + r * x_slab + hc * sizeof(T);
         const uint32_t c_off = u_region + x_region + r * c_slab + hc * sizeof(TC);
         const uint32_t g_off = u_region + x_region + c_region + r * g_slab + hc * sizeof(T);
-
-        auto load_pad = [&](int64_t m_first) -> uint32_t {
-            uint32_t bits = 0;
-            if (has_pad && active) {
-                const uint8_t *q = pp + m_first * pstep;
-#pragma unroll
-                for (int ts = 0; ts < kTS; ++ts)
-                    if (m_first + ts < L) bits |= (q[ts * pstep] ? 1u : 0u) << ts;
-            }
-            return bits;
-        };
+        const uint32_t pad_off = in_region + r * SS;                 // this row's flags of the stage
 
         // One block of kTS steps.  LAST marks the final block (ragged, and holding the step whose
         // predecessor state is c_init); all other blocks are full and branch-free.
@@ -371,7 +373,7 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const __grid_constant__ Sca
 #pragma unroll
             for (int ts = 0; ts < kTS; ++ts) {
                 if (LAST && ts >= steps) break;
-                const bool pad = PAD && ((pad_bits >> ts) & 1u);
+                const bool pad = PAD && ((pad_bits >> (8 * ts)) & 0xffu);
                 const bool at_start = LAST && (ts == steps - 1);
                 const int sl = slab + ts * dslab;
                 const Pack<T, V * K> up = lds_pack<Pack<T, V * K>>(sb + u_off + sl * su);
@@ -388,15 +390,20 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const __grid_constant__ Sca
                     const float xv = (K == 4) ? Cvt<T>::to_f(up.v[i * K + K - 1]) : Cvt<T>::to_f(xp.v[i]) * scale;
                     const float cprev = at_start ? c0[i] : Cvt<TC>::to_f(cpp.v[i]);
                     const float gh = Cvt<T>::to_f(ghp.v[i]);
-                    const float g1 = G::eval(cprev, wc1n[i], u1, b1n[i]);
-                    const float g2 = G::eval(cprev, wc2n[i], u2, b2n[i]);
+                    float omg1, omg2;   // 1 - g1, 1 - g2 (fp32 storage only)
+                    const float g1 = G::eval_pair(cprev, wc1n[i], u1, b1n[i], &omg1);
+                    const float g2 = G::eval_pair(cprev, wc2n[i], u2, b2n[i], &omg2);
                     const float dc = cprev - u0;
                     const float cv = fmaf(dc, g1, u0);
                     const float ghm = gh * mk[i];
-                    float gg2 = ghm * (cv - xv) * (g2 - g2 * g2);
                     const float gc = fmaf(ghm, g2, cur[i]);
-                    float gg1 = gc * dc * (g1 - g1 * g1);
-                    float gu0 = fmaf(-gc, g1, gc);
+                    // g(1-g) and gc(1-g1): from the exact complement for fp32 storage, one fused
+                    // multiply-add each for 16-bit storage (whose rounding hides the difference)
+                    const float dg1 = G::kPair ? g1 * omg1 : fmaf(-g1, g1, g1);
+                    const float dg2 = G::kPair ? g2 * omg2 : fmaf(-g2, g2, g2);
+                    float gg2 = ghm * (cv - xv) * dg2;
+                    float gg1 = gc * dc * dg1;
+                    float gu0 = G::kPair ? gc * omg1 : fmaf(-gc, g1, gc);
                     float gxv = fmaf(-ghm, g2, gh);
                     const float curn = fmaf(gc, g1, G::kUnfold * fmaf(gg1, wc1n[i], gg2 * wc2n[i]));
                     if (PAD) {
@@ -427,7 +434,7 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const __grid_constant__ Sca
         };
 
         auto run = [&](auto pad_c) {
-            uint32_t pad0 = load_pad(0), pad1 = load_pad(kTS);
+            constexpr bool PADF = decltype(pad_c)::value;
             int s = 0;
             uint32_t ph = 0;
             int64_t m = 0;   // backward step of the next block
@@ -438,11 +445,9 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const __grid_constant__ Sca
                 }
                 const uint32_t sb = order_after_wait(smem_u32(stage0) + (uint32_t)s * stage_bytes);
                 for (int q = 0; q < SS && m < L; q += kTS, m += kTS) {
-                    const uint32_t pad_cur = pad0;
-                    pad0 = pad1;
-                    pad1 = load_pad(m + 2 * kTS);
                     if (active) {
                         const int slab = asc ? q : (SS - 1 - q);
+                        const uint32_t pad_cur = PADF ? pad_word(sb + pad_off, q, SS, asc) : 0u;
                         const int64_t left = L - m;   // steps left including this block
                         if (left > kTS) block(sb, slab, asc ? 1 : -1, pad_cur, kTS, pad_c, BoolC<false>{});
                         else block(sb, slab, asc ? 1 : -1, pad_cur, (int)left, pad_c, BoolC<true>{});
@@ -538,7 +543,7 @@ static int make_scan_map(CUtensorMap *map, const void *base, int64_t row_bytes, 
 
 // Chooses V, the tile and the ring.  Returns false when the shape is not eligible.
 static bool choose_tile(int64_t L, int64_t B, int64_t d, int dirs, int k, int skip_type, int dtype,
-                        int c_dtype, bool backward, TileCfg *out) {
+                        int c_dtype, bool backward, bool has_pad, TileCfg *out) {
     const int s = (int)dtype_size(dtype);
     if (dtype == SRU_F64 || s == 0) return false;
     const int granule = 16 / s;  // elements per 16 bytes
@@ -546,18 +551,36 @@ static bool choose_tile(int64_t L, int64_t B, int64_t d, int dirs, int k, int sk
     const int64_t D = d * dirs, ncols = B * D;
     const int sms = num_sms();
     const int vmax = 4, vmin = 1;
-    // Columns per thread, from sweeps on B200: V = 4 amortises the per-step overhead best once it
-    // still leaves eight or more warps per SM; below that the scan is bound by per-step latency
-    // and V = 2 (twice the warps) wins.  With fewer than four warps of columns per SM the forward
-    // does best with V = 1 (a lone warp issues one column's step in less time than two); the backward,
-    // with twice the reads per step, never did, and V = 8 never did anywhere.
-    int v = (ncols / (32 * 4) >= (int64_t)sms * 8) ? 4 : 2;
-    if (!backward && ncols / 128 < (int64_t)sms * 4) v = 1;
+    // Columns per thread (V) and consumer threads per CTA, from sweeps on B200 keyed by w = warps of
+    // columns per SM.  Plenty of warps: V = 4 (8 bytes of every tensor per thread and step) amortises
+    // the per-step overhead best.  Few warps: each warp is alone on its scheduler and bound by the
+    // latency of its own instruction stream, so narrower threads (more warps) win, down to V = 1.
+    // The backward, with twice the reads per step, moves to fatter CTAs earlier; fp32 columns carry
+    // twice the bytes, so their V is about half.  V = 8 never won anywhere.
+    const int64_t w = ncols / (32 * (int64_t)sms);
+    int v, ntc;
+    if (s == 2) {
+        if (!backward) {
+            if (w >= 20) { v = 4; ntc = 64; }
+            else if (w >= 10) { v = has_pad ? 2 : 4; ntc = has_pad ? 64 : 128; }
+            else if (w >= 5) { v = 1; ntc = 64; }
+            else { v = 1; ntc = 128; }
+        } else {
+            if (w >= 80) { v = 4; ntc = 64; }
+            else if (w >= 40) { v = 2; ntc = 128; }
+            else if (w >= 20) { v = 4; ntc = 128; }
+            else if (w >= 10) { v = has_pad ? 2 : 4; ntc = has_pad ? 64 : 128; }
+            else { v = 1; ntc = 64; }
+        }
+    } else {
+        if (!backward) { v = (w >= 20) ? 2 : 1; ntc = 128; }
+        else if (w >= 80) { v = 2; ntc = 64; }
+        else if (w >= 20) { v = 4; ntc = 64; }
+        else { v = 2; ntc = 128; }
+    }
+    while (ntc > 32 && ncols / ((int64_t)v * ntc) < (int64_t)sms / 2) ntc /= 2;   // tiny problems: spread over the SMs
     v = env_int(backward ? "SRU_B200_BWD_V" : "SRU_B200_FWD_V", v);
     if (v < vmin || v > vmax || (v & (v - 1))) return false;
-    // consumer threads per CTA: two warps, one when that is needed to give every SM a CTA
-    int ntc = (ncols / ((int64_t)v * 64) >= (int64_t)sms) ? 64 : 32;
-    if (v == 1 && ncols / 128 >= (int64_t)sms * 3 / 4) ntc = 128;   // one CTA of four warps per SM
     ntc = env_int("SRU_B200_SCAN_THREADS", ntc);
     if (ntc < 32 || ntc > 128 || ntc % 32) return false;
     // hidden width of the tile: largest divisor of d, multiple of the granule, <= v*ntc, and with a
@@ -569,6 +592,7 @@ static bool choose_tile(int64_t L, int64_t B, int64_t d, int dirs, int k, int sk
     if (hw == 0) return false;
     const int tpr = hw / v;
     int br = (int)std::min<int64_t>(B, std::max(1, ntc / tpr));
+    if (has_pad) br = std::min(br, 32 * kPadPerLane / kTS);   // the producer warp stages rows x steps <= 256 flags
     const int cthreads = ((br * tpr + 31) / 32) * 32;
     if (cthreads > 128) return false;
     const bool has_x = (k == 3 && skip_type == 1);
@@ -584,9 +608,11 @@ static bool choose_tile(int64_t L, int64_t B, int64_t d, int dirs, int k, int sk
     while (ss < 32 && (size_t)ss * br * per_row_step < 16 * 1024 && (size_t)(2 * ss) * br * per_row_step * 3 <= ring0) ss *= 2;
     ss = env_int("SRU_B200_SCAN_SS", ss);
     if (ss < kTS || ss > 64 || ss % kTS) return false;
+    while (has_pad && br * ss > 32 * kPadPerLane) ss -= kTS;
     auto stage_size = [&](int steps) {
         size_t t = align128((uint32_t)(steps * br * hw * k * s)) + align128((uint32_t)(has_x ? steps * br * hw * s : 0));
         if (backward) t += align128((uint32_t)(steps * br * hw * sc)) + align128((uint32_t)(steps * br * hw * s));
+        if (has_pad) t += align128((uint32_t)(steps * br));
         return t;
     };
     const size_t stage_bytes = stage_size(ss);
@@ -668,7 +694,7 @@ int launch_scan_pipelined(const ScanArgs &a, bool backward, cudaStream_t st) {
     if (!err) return set_error(SRU_ERR_CUDA, "device error flag unavailable");
     PipeArgs p;
     p.a = a;
-    if (!choose_tile(a.L, a.B, a.d, a.dirs, a.k, a.skip_type, a.dtype, a.c_dtype, backward, &p.c)) return 0;
+    if (!choose_tile(a.L, a.B, a.d, a.dirs, a.k, a.skip_type, a.dtype, a.c_dtype, backward, a.mask_pad != nullptr, &p.c)) return 0;
     p.err = err;
 
     // The tensor-map encoder is a driver entry point: make sure this thread has the primary context.
