@@ -347,7 +347,7 @@ def main():
     e1.record()
     barrier()
     ms_total = max_over_ranks(e0.elapsed_time(e1))
-    launches = (_lib.launch_count - launches0) // max(1, args.steps)
+    launches = _lib.launch_count - launches0          # this rank's own kernels inside the timed region
     clocks = sampler.stop() if sampler else None
     ms_per_step = ms_total / args.steps
     value = tokens_global / (ms_per_step / 1e3)
@@ -409,7 +409,7 @@ def main():
         t = cands[top]
         # DRAM traffic per launch: ratio of measured dram bytes to algorithmic bytes from the ncu captures
         # summarised under profiles/ (small case of the same kernels), applied to this run's units.
-        ratio = {"scan_fwd": 0.93, "scan_fwd_infer": 0.93, "scan_bwd": 0.97, "gemm_all": 0.85}.get(top)
+        ratio = {"scan_fwd": 0.93, "scan_fwd_infer": 0.93, "scan_bwd": 0.97, "gemm_all": 0.89}.get(top)
         alg = {"scan_fwd": work["scan_fwd_bytes"], "scan_fwd_infer": work["scan_fwd_bytes"],
                "scan_bwd": work["scan_bwd_bytes"], "gemm_all": work["gemm_bytes"]}.get(top)
         if top == "gemm_all":
@@ -435,6 +435,7 @@ def main():
         "e2e": {"value": tokens_global / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": result_bytes},
         "gpu_launches": launches,
+        "gpu_launches_per_step": launches // max(1, args.steps),
         "clocks": clocks,
         "roofline": roofline,
         "kernels": kernels,
