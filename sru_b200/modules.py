@@ -20,7 +20,7 @@ from torch.nn.utils.rnn import PackedSequence
 
 from . import _lib
 from . import ops
-from .projection import project
+from .projection import GradLink, grad_link_enabled, project
 
 
 def _load_scripted_ops() -> bool:
@@ -223,6 +223,8 @@ class SRUCell(nn.Module):
         if self.training and (self.dropout > 0):
             mask_c = self.get_dropout_mask_((batch_size, self.output_size), self.dropout)
 
+        if not torch.jit.is_scripting():
+            self._begin_grad_link(input, residual)
         U, V = self.compute_UV(input, c0, mask_pad)
         h, c = self.apply_recurrence(U, V, residual, c0, scale_val, mask_c, mask_pad)
         if self.layer_norm is not None and self.normalize_after:
@@ -240,12 +242,24 @@ class SRUCell(nn.Module):
                                                     self.has_skip_term, scale_val, mask_c, mask_pad)
 
     @torch.jit.unused
+    def _begin_grad_link(self, input: Tensor, residual: Tensor) -> None:
+        """A k = 3 layer whose GEMM operand and highway input are one tensor gets a GradLink: the two
+        gradients of that tensor are then summed in the dgrad GEMM's epilogue instead of by autograd."""
+        self._grad_link = None
+        if (grad_link_enabled() and input is residual and self.custom_m is None and self.weight_proj is None
+                and self.has_skip_term and self.num_matrices == 3 and input.is_cuda
+                and torch.is_grad_enabled() and input.requires_grad):
+            self._grad_link = GradLink()
+
+    @torch.jit.unused
     def _apply_recurrence_eager(self, U: Tensor, V: Tensor, residual: Tensor, c0: Tensor,
                                 scale_val: Optional[Tensor], mask_c: Optional[Tensor],
                                 mask_pad: Optional[Tensor]) -> List[Tensor]:
+        link, self._grad_link = getattr(self, "_grad_link", None), None
         return ops.elementwise_recurrence_gpu(U, residual, V, self.bias, c0, self.activation_type,
                                               self.hidden_size, self.bidirectional, self.has_skip_term,
-                                              scale_val, mask_c, mask_pad, self.amp_recurrence_fp16)
+                                              scale_val, mask_c, mask_pad, self.amp_recurrence_fp16,
+                                              grad_link=link)
 
     def compute_UV(self, input: Tensor, c0: Optional[Tensor],
                    mask_pad: Optional[Tensor]) -> Tuple[Tensor, Tensor]:
@@ -281,7 +295,7 @@ class SRUCell(nn.Module):
     def _compute_U_eager(self, x: Tensor) -> Tensor:
         if self.weight_proj is not None:
             return project(project(x, self.weight_proj), self.weight)
-        return project(x, self.weight)
+        return project(x, self.weight, link=getattr(self, "_grad_link", None))
 
     def get_dropout_mask_(self, size: Tuple[int, int], p: float) -> Tensor:
         """Inverted-dropout mask shared over time (sru/modules.py:380-387)."""

@@ -152,7 +152,7 @@ class ElementwiseRecurrence(Function):
 
     @staticmethod
     def forward(ctx, u, x, weight_c, bias, init, activation_type, d_out, bidirectional,
-                has_skip_term, scale_x, mask_c=None, mask_pad=None):
+                has_skip_term, scale_x, mask_c=None, mask_pad=None, grad_link=None):
         length, batch, dirs, k, skip_type, is_custom = _geometry(u, x, d_out, bidirectional,
                                                                  has_skip_term, weight_c)
         st = u.dtype
@@ -174,6 +174,10 @@ class ElementwiseRecurrence(Function):
         ctx.shapes = (u.shape, x.shape, x.dtype, weight_c.shape, weight_c.dtype, bias.dtype,
                       init.shape, init.dtype)
         ctx.save_for_backward(u_c, x_c, wc_c, bias_c, init_c, mask_c_c, pad_c, c_hist)
+        # an armed link takes grad_x to the projection's backward (see projection.GradLink); only when the
+        # scan reads x as it is, so that its grad_x is the gradient of that very tensor
+        ctx.link = grad_link if (grad_link is not None and grad_link.armed and skip_type == 1
+                                 and x.dtype == st and x.is_contiguous()) else None
         if x.dim() == 2:
             h = h.squeeze(0)
         return h, c_last.to(init.dtype) if init.dtype != c_last.dtype else c_last
@@ -193,10 +197,13 @@ class ElementwiseRecurrence(Function):
             length, batch, d, dirs, k, act, skip_type, is_custom, scale)
         grad_u = grad_u.view(u_shape)
         if grad_x is not None:
-            grad_x = grad_x.view(x_shape).to(x_dtype)
+            if ctx.link is not None:
+                ctx.link.grad_x, grad_x = grad_x, None    # the projection's backward adds its dgrad onto it
+            else:
+                grad_x = grad_x.view(x_shape).to(x_dtype)
         grad_wc = grad_wc.view(wc_shape).to(wc_dtype)
         return (grad_u, grad_x, grad_wc, grad_bias.to(bias_dtype), grad_init.view(init_shape).to(init_dtype),
-                None, None, None, None, None, None, None)
+                None, None, None, None, None, None, None, None)
 
 
 def elementwise_recurrence_forward(u: Tensor, x: Tensor, weight_c: Tensor, bias: Tensor, init: Tensor,
@@ -228,8 +235,10 @@ def elementwise_recurrence_gpu(U: Tensor, x: Tensor, weight_c: Tensor, bias: Ten
                                has_skip_term: bool, scale_x: Optional[Tensor] = None,
                                dropout_mask_c: Optional[Tensor] = None,
                                mask_pad: Optional[Tensor] = None,
-                               amp_recurrence_fp16: bool = False) -> List[Tensor]:
-    """Elementwise recurrence of SRU on the GPU; signature of sru/ops.py:98-110.
+                               amp_recurrence_fp16: bool = False,
+                               grad_link=None) -> List[Tensor]:
+    """Elementwise recurrence of SRU on the GPU; signature of sru/ops.py:98-110, plus ``grad_link``
+    (a projection.GradLink armed by the projection that produced U from the same x; optional).
 
     Returns ``[h, last_c]``.  In "reference" amp mode the casts of sru/ops.py:116-127 are
     applied first, so dtypes of the results equal the reference's; in "native" mode (default)
@@ -242,6 +251,7 @@ def elementwise_recurrence_gpu(U: Tensor, x: Tensor, weight_c: Tensor, bias: Ten
         else:
             cast = torch.Tensor.float
         U, x, c_init = cast(U), cast(x), cast(c_init)
+        grad_link = None      # x is a cast copy here: its gradient is not the GEMM operand's
     if not torch.is_grad_enabled() or not any(
             t is not None and t.requires_grad for t in (U, x, weight_c, bias, c_init)):
         h, c_last, _ = _forward_nograd(U, x, weight_c, bias, c_init, activation_type, hidden_size,
@@ -249,7 +259,7 @@ def elementwise_recurrence_gpu(U: Tensor, x: Tensor, weight_c: Tensor, bias: Ten
         return [h, c_last.to(c_init.dtype)]
     return list(ElementwiseRecurrence.apply(U, x, weight_c, bias, c_init, activation_type, hidden_size,
                                             bidirectional, has_skip_term, scale_x, dropout_mask_c,
-                                            mask_pad))
+                                            mask_pad, grad_link))
 
 
 def _forward_nograd(U, x, weight_c, bias, c_init, activation_type, hidden_size, bidirectional,

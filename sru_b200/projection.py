@@ -69,12 +69,47 @@ def gemm(a: Tensor, b: Tensor, trans_a: bool = False, trans_b: bool = False,
     return out
 
 
+_grad_link_on = True
+
+
+def set_grad_link_enabled(flag: bool) -> None:
+    """Switches the fused gradient sum of a layer input (GradLink) on or off; on by default.  Off, autograd
+    adds the scan's and the GEMM's gradient of the input itself (one more pass over the tensor)."""
+    global _grad_link_on
+    _grad_link_on = bool(flag)
+
+
+def grad_link_enabled() -> bool:
+    return _grad_link_on
+
+
+class GradLink:
+    """Joins the two gradients of a layer input.
+
+    A k = 3 layer uses its input twice: as the GEMM operand (U = x W) and as the highway term of
+    the scan.  Autograd would materialise both gradients and add them with one more pass over
+    (length, batch, width).  With a link, the scan's backward leaves its grad_x here instead of
+    returning it, and the projection's backward, which always runs later (U feeds the scan),
+    lets the dgrad GEMM accumulate onto that buffer in its epilogue and returns the sum.
+
+    ``armed`` is set by project() when the tensor it was given goes into the GEMM as it is (same
+    storage and dtype), i.e. when "gradient of the GEMM operand" and "gradient of x" are the same
+    thing; the scan side only uses an armed link.
+    """
+    __slots__ = ("armed", "grad_x")
+
+    def __init__(self):
+        self.armed = False
+        self.grad_x = None
+
+
 class _Projection(Function):
     @staticmethod
-    def forward(ctx, x, w, col_bias):
+    def forward(ctx, x, w, col_bias, link):
         # x (M, K), w (K, N), both already in the 16-bit compute dtype
         ctx.save_for_backward(x, w)
         ctx.has_bias = col_bias is not None
+        ctx.link = link
         return gemm(x, w, col_bias=col_bias)
 
     @staticmethod
@@ -82,18 +117,30 @@ class _Projection(Function):
         x, w = ctx.saved_tensors
         grad_u = grad_u.contiguous()
         gx = gw = gb = None
+        highway = None
+        if ctx.link is not None:
+            highway, ctx.link.grad_x = ctx.link.grad_x, None
         if ctx.needs_input_grad[0]:
-            gx = gemm(grad_u, w, trans_b=True)            # (M,N) x (K,N)^T -> (M,K)
+            if highway is not None and highway.dtype == x.dtype and highway.numel() == x.numel() \
+                    and highway.is_contiguous():
+                # (M,N) x (K,N)^T added onto the scan's highway gradient in the epilogue
+                gx = gemm(grad_u, w, trans_b=True, out=highway.view(x.shape), accumulate=True)
+            else:
+                gx = gemm(grad_u, w, trans_b=True)        # (M,N) x (K,N)^T -> (M,K)
+                if highway is not None:
+                    gx = gx + highway.reshape(gx.shape).to(gx.dtype)
         if ctx.needs_input_grad[1]:
             gw = gemm(x, grad_u, trans_a=True)            # (M,K)^T x (M,N) -> (K,N)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             gb = grad_u.float().sum(0)
-        return gx, gw, gb
+        return gx, gw, gb, None
 
 
-def project(x: Tensor, w: Tensor, col_bias: Optional[Tensor] = None) -> Tensor:
+def project(x: Tensor, w: Tensor, col_bias: Optional[Tensor] = None,
+            link: Optional[GradLink] = None) -> Tensor:
     """x (M, K) @ w (K, N) with autograd.  Follows autocast: inside an autocast region the
-    operands are cast to the autocast dtype, as ``Tensor.mm`` would be."""
+    operands are cast to the autocast dtype, as ``Tensor.mm`` would be.  ``link`` (see GradLink)
+    is armed when x itself becomes the GEMM operand and x needs a gradient."""
     if not x.is_cuda:
         raise _lib.SruB200Error("sru_b200 has no CPU path: the projection input must be a CUDA tensor")
     dt = x.dtype
@@ -107,8 +154,10 @@ def project(x: Tensor, w: Tensor, col_bias: Optional[Tensor] = None) -> Tensor:
         xc = xc if xc.is_contiguous() else xc.contiguous()
         wc = wc if wc.is_contiguous() else wc.contiguous()
         if _tma_compatible(xc, wc):
+            if link is not None:
+                link.armed = xc is x and x.requires_grad and torch.is_grad_enabled()
             with torch.autocast("cuda", enabled=False):
-                return _Projection.apply(xc, wc, col_bias)
+                return _Projection.apply(xc, wc, col_bias, link if link is not None and link.armed else None)
     out = x.mm(w) if x.dtype == w.dtype or torch.is_autocast_enabled("cuda") else x.to(dt).mm(w)
     if col_bias is not None:
         out = out + col_bias.to(out.dtype)

@@ -127,6 +127,57 @@ def test_autocast_native_and_reference_modes(amp_dtype):
             assert rel_err(p.grad, ref_grads[n]) <= 2e-2, (mode, n, rel_err(p.grad, ref_grads[n]))
 
 
+@pytest.mark.parametrize("amp_dtype", [torch.bfloat16, torch.float16])
+def test_grad_link_equals_autograd_sum(amp_dtype, monkeypatch):
+    """Layers 1.. of a k = 3 stack use their input as GEMM operand and as highway term.  With the gradient
+    link the dgrad GEMM accumulates onto the scan's grad_x; without it autograd adds the two.  Same gradients
+    (one 16-bit rounding apart), and both within 2e-2 of the fp32 CPU oracle."""
+    import sru_b200
+    from sru_b200 import projection
+    torch.manual_seed(5)
+    SRU = _sru()
+    model = SRU(input_size=64, hidden_size=64, num_layers=3, bidirectional=True, dropout=0.0).to(DEV).train()
+    L, B = 19, 8
+    x0 = torch.randn(L, B, 64, device=DEV)
+    lens = torch.randint(9, L + 1, (B,))
+    mp = (torch.arange(L).view(L, 1) >= lens.view(1, B)).to(DEV)
+    cpu = to_oracle(model).train()
+    xr = x0.cpu().requires_grad_(True)
+    h_ref, _ = cpu(xr, mask_pad=mp.cpu())
+    (h_ref * h_ref).sum().backward()
+    ref = {n: p.grad for n, p in cpu.named_parameters()}
+    ref["x"] = xr.grad
+
+    accumulating = []
+    real_gemm = projection.gemm
+
+    def spy(*a, **kw):
+        accumulating.append(bool(kw.get("accumulate", False)))
+        return real_gemm(*a, **kw)
+    monkeypatch.setattr(projection, "gemm", spy)
+
+    got = {}
+    for on in (True, False):
+        projection.set_grad_link_enabled(on)
+        accumulating.clear()
+        try:
+            model.zero_grad()
+            x = x0.clone().requires_grad_(True)
+            with torch.autocast("cuda", dtype=amp_dtype):
+                h, _ = model(x, mask_pad=mp)
+                loss = (h.float() ** 2).sum()
+            loss.backward()
+        finally:
+            projection.set_grad_link_enabled(True)
+        # two of the three layers (128 -> 128, k = 3) qualify; the first (64 -> 128, k = 4) does not
+        assert sum(accumulating) == (2 if on else 0), (on, accumulating)
+        got[on] = {n: p.grad.clone() for n, p in model.named_parameters()}
+        got[on]["x"] = x.grad.clone()
+    for n in got[True]:
+        assert rel_err(got[True][n], got[False][n]) <= 1e-2, (n, rel_err(got[True][n], got[False][n]))
+        assert rel_err(got[True][n], ref[n]) <= 2e-2, (n, rel_err(got[True][n], ref[n]))
+
+
 def test_dropout_mask_is_an_input():
     """With the same RNG state the training-mode dropout mask equals the oracle model's."""
     torch.manual_seed(2)
