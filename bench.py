@@ -91,6 +91,7 @@ def algorithmic_work(cfg, B, s_bytes, c_bytes):
     fwd = bwd = 0
     flops_f = flops_b = 0
     gemm_bytes = 0
+    ln_f = ln_b = 0
     for li, (n_in, D, k, dirs, p) in enumerate(layer_shapes(cfg["kwargs"])):
         cols = L * B * D
         e3 = 1 if k == 3 else 0
@@ -109,8 +110,16 @@ def algorithmic_work(cfg, B, s_bytes, c_bytes):
             gemm_bytes += once * (3 if (cfg["train"] and (li > 0 or (m_, k_, n_) != prods[0])) else (2 if cfg["train"] else 1))
         if cfg["train"]:
             flops_b += 2 * f if li > 0 else (2 * f - (2 * M * n_in * (p if p else D * k)))
+        if cfg["kwargs"].get("layer_norm"):
+            # layer normalisation: forward reads x, writes y; backward reads dy and x, writes dx
+            after = cfg["kwargs"].get("normalize_after", False)
+            n_ln = D if after else n_in
+            sx = s_bytes if (after or li > 0) else 4          # the first layer's input is the fp32 batch
+            sy = s_bytes
+            ln_f += M * n_ln * (sx + sy)
+            ln_b += M * n_ln * (sy + 2 * sx)
     return dict(scan_fwd_bytes=fwd, scan_bwd_bytes=bwd, gemm_fwd_flops=flops_f, gemm_bwd_flops=flops_b,
-                gemm_bytes=gemm_bytes)
+                gemm_bytes=gemm_bytes, ln_fwd_bytes=ln_f, ln_bwd_bytes=ln_b)
 
 
 class ClockSampler:
@@ -393,6 +402,12 @@ def main():
                        peak=peaks["hbm_gbs"])
         elif name == "scan_bwd":
             ent.update(bound="hbm", achieved=work["scan_bwd_bytes"] / (per_step_ms * 1e6), unit="GB/s",
+                       peak=peaks["hbm_gbs"])
+        elif name == "layer_norm_fwd" and work["ln_fwd_bytes"]:
+            ent.update(bound="hbm", achieved=work["ln_fwd_bytes"] / (per_step_ms * 1e6), unit="GB/s",
+                       peak=peaks["hbm_gbs"])
+        elif name == "layer_norm_bwd" and work["ln_bwd_bytes"]:
+            ent.update(bound="hbm", achieved=work["ln_bwd_bytes"] / (per_step_ms * 1e6), unit="GB/s",
                        peak=peaks["hbm_gbs"])
         ent["frac"] = ent["achieved"] / ent["peak"] if "achieved" in ent else None
         kernels[name] = ent

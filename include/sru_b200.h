@@ -198,6 +198,45 @@ int sru_b200_gemm_ws(
     int trans_a, int trans_b, int ab_dtype, int c_dtype, int accumulate,
     void *workspace, size_t workspace_bytes, void *stream);
 
+/*
+ * Layer normalisation over the last dimension: the nn.LayerNorm an SRU layer applies to its input
+ * (sru/modules.py:252-253) or to its output (:278-279; constructed at :155-160 with the default
+ * eps 1e-5 and an affine weight and bias).  In the reference this is a library operator (ATen's
+ * layer_norm); its published definition is
+ *
+ *   y[r, :] = (x[r, :] - mean_r) * rstd_r * gamma + beta,     rstd_r = 1 / sqrt(var_r + eps),
+ *
+ * mean_r and the biased variance var_r taken over the n elements of row r.
+ *
+ *   x (rows, n)   SRU_F32, SRU_F16 or SRU_BF16, rows contiguous
+ *   y (rows, n)   x's type; or SRU_F16 / SRU_BF16 with fp32 x, which writes the normalised rows
+ *                 directly in the type the projection GEMM consumes (one rounding, as casting an
+ *                 fp32 result would)
+ *   gamma, beta   float[n], either may be NULL (ones / zeros)
+ *   mean, rstd    float[rows], out; needed by the backward pass, either may be NULL
+ *   n             a multiple of 8 (16-bit x) or 4 (fp32 x), at most 4096: other row lengths get
+ *                 SRU_ERR_UNSUPPORTED
+ */
+int sru_b200_layer_norm_forward(
+    void *y, float *mean, float *rstd, const void *x, const float *gamma, const float *beta,
+    int64_t rows, int64_t n, double eps, int x_dtype, int y_dtype, void *stream);
+
+/* Scratch of the backward pass: per-CTA column sums, at most 4 * (number of SMs) * 2 * n floats. */
+size_t sru_b200_layer_norm_backward_workspace_bytes(int64_t rows, int64_t n);
+
+/*
+ * Backward of the above (what autograd derives for nn.LayerNorm in the reference):
+ *   dx = (dy*gamma - mean_n(dy*gamma) - xhat * mean_n(dy*gamma*xhat)) * rstd,  xhat = (x - mean) * rstd
+ *   dgamma = sum over rows of dy * xhat,   dbeta = sum over rows of dy
+ * dy has y's type, dx has x's type; dgamma / dbeta are float[n] and either may be NULL.  The column
+ * sums are formed in a fixed order (no atomics): repeated calls give identical bits.
+ */
+int sru_b200_layer_norm_backward(
+    void *dx, float *dgamma, float *dbeta, const void *dy, const void *x,
+    const float *mean, const float *rstd, const float *gamma,
+    int64_t rows, int64_t n, int x_dtype, int y_dtype,
+    void *workspace, size_t workspace_bytes, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,8 +1,8 @@
 """CPU execution of the SRU layer stack with the oracle scan.  TEST INFRASTRUCTURE ONLY.
 
 Reuses the package's host-side module classes for parameters and layer plumbing, and
-replaces the two device operations with CPU ones: the projection becomes ``Tensor.mm``
-and the recurrence becomes the C oracle (after the casts of sru/ops.py:116-127, i.e. the
+replaces the device operations with CPU ones: the projection becomes ``Tensor.mm``, the layer
+normalisation and the recurrence become the C oracle (after the casts of sru/ops.py:116-127, i.e. the
 recurrence always runs in float32 unless the tensors are float64).  This is the CPU
 baseline that the benchmark times and the model-level checker of the GPU tests.
 """
@@ -29,6 +29,14 @@ class OracleSRUCell(SRUCell):
         if self.weight_proj is not None:
             return x.mm(self.weight_proj).mm(self.weight)
         return x.mm(self.weight)
+
+    def _layer_norm_eager(self, t, before_projection):
+        ln = self.layer_norm
+        dt = torch.float64 if t.dtype == torch.float64 else torch.float32
+        return sru_oracle.layer_norm_oracle(t.to(dt), ln.weight, ln.bias, ln.eps)
+
+    def _begin_grad_link(self, input, residual):
+        self._grad_link = None
 
 
 class OracleSRU(SRU):

@@ -152,3 +152,57 @@ def elementwise_recurrence_oracle(U, x, weight_c, bias, c_init, activation_type:
     if x.dim() == 2:
         h = h.squeeze(0)
     return h, c_last
+
+
+def layer_norm_forward(x2d, gamma, beta, eps):
+    """(rows, n) -> (y, mean, rstd) on CPU in x2d's dtype (float32 or float64)."""
+    dtype = x2d.dtype
+    sfx, _ = _suffix_and_real(dtype)
+    x2d = _prep(x2d, dtype)
+    gamma, beta = _prep(gamma, dtype), _prep(beta, dtype)
+    rows, n = x2d.shape
+    y = torch.empty_like(x2d)
+    mean = torch.empty(rows, dtype=dtype)
+    rstd = torch.empty(rows, dtype=dtype)
+    getattr(lib(), "sru_oracle_layer_norm_forward" + sfx)(
+        _p(y), _p(mean), _p(rstd), _p(x2d), _p(gamma), _p(beta),
+        ctypes.c_long(rows), ctypes.c_long(n), ctypes.c_double(float(eps)))
+    return y, mean, rstd
+
+
+def layer_norm_backward(dy2d, x2d, mean, rstd, gamma):
+    """-> (dx, dgamma, dbeta) on CPU in x2d's dtype."""
+    dtype = x2d.dtype
+    sfx, _ = _suffix_and_real(dtype)
+    x2d, dy2d = _prep(x2d, dtype), _prep(dy2d, dtype)
+    mean, rstd, gamma = _prep(mean, dtype), _prep(rstd, dtype), _prep(gamma, dtype)
+    rows, n = x2d.shape
+    dx = torch.empty_like(x2d)
+    dg = torch.empty(n, dtype=dtype)
+    db = torch.empty(n, dtype=dtype)
+    getattr(lib(), "sru_oracle_layer_norm_backward" + sfx)(
+        _p(dx), _p(dg), _p(db), _p(dy2d), _p(x2d), _p(mean), _p(rstd), _p(gamma),
+        ctypes.c_long(rows), ctypes.c_long(n))
+    return dx, dg, db
+
+
+class _OracleLayerNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gamma, beta, eps):
+        x2d = x.detach().contiguous().view(-1, x.size(-1))
+        y, mean, rstd = layer_norm_forward(x2d, gamma, beta, eps)
+        ctx.save_for_backward(x2d, mean, rstd, gamma)
+        ctx.shape = x.shape
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2d, mean, rstd, gamma = ctx.saved_tensors
+        dx, dg, db = layer_norm_backward(dy.contiguous().view(x2d.shape), x2d, mean, rstd, gamma)
+        return dx.view(ctx.shape), dg, db, None
+
+
+def layer_norm_oracle(x, gamma, beta, eps=1e-5):
+    """Differentiable CPU layer norm over the last dimension (float32 or float64 tensors)."""
+    dt = x.dtype
+    return _OracleLayerNorm.apply(x, gamma.to(dt), beta.to(dt), eps)

@@ -20,7 +20,8 @@ from torch.nn.utils.rnn import PackedSequence
 
 from . import _lib
 from . import ops
-from .projection import GradLink, grad_link_enabled, project
+from .layer_norm import layer_norm
+from .projection import GradLink, gemm_backend, grad_link_enabled, project
 
 
 def _load_scripted_ops() -> bool:
@@ -212,7 +213,10 @@ class SRUCell(nn.Module):
 
         residual = input
         if self.layer_norm is not None and not self.normalize_after:
-            input = self.layer_norm(input)
+            if not torch.jit.is_scripting():
+                input = self._layer_norm_eager(input, True)
+            else:
+                input = self.layer_norm(input)
         if self.training and (self.rnn_dropout > 0):
             mask = self.get_dropout_mask_((batch_size, input.size(-1)), self.rnn_dropout)
             input = input * mask.expand_as(input)
@@ -228,8 +232,30 @@ class SRUCell(nn.Module):
         U, V = self.compute_UV(input, c0, mask_pad)
         h, c = self.apply_recurrence(U, V, residual, c0, scale_val, mask_c, mask_pad)
         if self.layer_norm is not None and self.normalize_after:
-            h = self.layer_norm(h)
+            if not torch.jit.is_scripting():
+                h = self._layer_norm_eager(h, False)
+            else:
+                h = self.layer_norm(h)
         return h, c
+
+    @torch.jit.unused
+    def _layer_norm_eager(self, t: Tensor, before_projection: bool) -> Tensor:
+        """The layer's nn.LayerNorm (sru/modules.py:252-253, :278-279) on this package's kernel.
+
+        Output type: before the projection, inside a 16-bit autocast region with the tcgen05 GEMM
+        and no input dropout, the normalised rows are written in the autocast type (they only feed the
+        GEMM, which would round them to that type anyway).  After the recurrence, native amp mode keeps
+        a 16-bit h in its type.  Otherwise the reference's types: float32 under autocast, else t's.
+        """
+        ln = self.layer_norm
+        out_dtype: Optional[torch.dtype] = None
+        if before_projection:
+            if (torch.is_autocast_enabled("cuda") and gemm_backend() == "tcgen05" and self.custom_m is None
+                    and not (self.training and self.rnn_dropout > 0)):
+                out_dtype = torch.get_autocast_dtype("cuda")
+        elif ops.get_amp_mode() == "native" and t.dtype in (torch.float16, torch.bfloat16):
+            out_dtype = t.dtype
+        return layer_norm(t, ln.weight, ln.bias, ln.eps, out_dtype)
 
     def apply_recurrence(self, U: Tensor, V: Tensor, residual: Tensor, c0: Tensor,
                          scale_val: Optional[Tensor], mask_c: Optional[Tensor],

@@ -38,3 +38,8 @@ def model_cases():
 @pytest.fixture(scope="session")
 def regression_case():
     return torch.load(os.path.join(GOLDEN, "regression_2_3_5.pt"), weights_only=False)
+
+
+@pytest.fixture(scope="session")
+def layer_norm_cases():
+    return torch.load(os.path.join(GOLDEN, "layer_norm_cases.pt"), weights_only=False)

@@ -16,6 +16,11 @@ What is recorded
 * ``regression_2_3_5.pt`` -- the tensors of the reference's regression artifact
   test/regression/artifacts/2.3.5.pt (its test: test/regression/test_regression.py:19-51),
   re-saved as a plain dict of tensors.
+* ``layer_norm_cases.pt`` -- the layer normalisation of a reference ``sru.SRUCell`` (the ``nn.LayerNorm``
+  it constructs at sru/modules.py:155-160 and calls at :252-253 / :278-279), float64, random affine
+  parameters: input, output, and the gradients autograd gives for input, weight and bias.
+
+``python tests/golden/make_golden.py layer_norm`` regenerates only the last file.
 """
 import os
 import sys
@@ -176,7 +181,35 @@ def make_regression():
     print("regression artifact:", out["version"], out["kwargs"])
 
 
+def make_layer_norm_cases():
+    cases = []
+    for i, (rows_shape, n, after) in enumerate([((7, 3), 8, False), ((9,), 120, False), ((2, 2), 512, False),
+                                                ((3,), 1024, True), ((1, 2), 2048, True), ((2,), 4096, True),
+                                                ((6, 2), 24, False), ((2,), 1000, False)]):
+        g = torch.Generator().manual_seed(900 + i)
+        hidden = n if not after else n
+        cell = sru.SRUCell(n if not after else 8, hidden, layer_norm=True, normalize_after=after).double()
+        ln = cell.layer_norm
+        assert isinstance(ln, torch.nn.LayerNorm) and ln.normalized_shape == (n,)
+        with torch.no_grad():
+            ln.weight.copy_(torch.randn(n, generator=g, dtype=torch.float64) * 0.5 + 1.0)
+            ln.bias.copy_(torch.randn(n, generator=g, dtype=torch.float64) * 0.3)
+        x = (torch.randn(*rows_shape, n, generator=g, dtype=torch.float64) * 1.7 + 0.4).requires_grad_(True)
+        dy = torch.randn(*rows_shape, n, generator=g, dtype=torch.float64)
+        y = ln(x)
+        y.backward(dy)
+        cases.append({"n": n, "eps": ln.eps, "x": x.detach().clone(), "weight": ln.weight.detach().clone(),
+                      "bias": ln.bias.detach().clone(), "dy": dy, "y": y.detach().clone(),
+                      "dx": x.grad.clone(), "dweight": ln.weight.grad.clone(), "dbias": ln.bias.grad.clone()})
+    torch.save(cases, os.path.join(OUT, "layer_norm_cases.pt"))
+    print("layer_norm_cases:", len(cases))
+
+
 if __name__ == "__main__":
-    make_op_cases()
-    make_model_cases()
-    make_regression()
+    if sys.argv[1:] == ["layer_norm"]:
+        make_layer_norm_cases()
+    else:
+        make_op_cases()
+        make_model_cases()
+        make_regression()
+        make_layer_norm_cases()

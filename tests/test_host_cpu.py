@@ -46,7 +46,14 @@ def test_model_cases_through_oracle(model_cases):
         assert (c - case["c"]).abs().max() <= 1e-5, case["name"]
         for n, p in model.named_parameters():
             if n in case["grads"]:
-                assert rel_err(p.grad, case["grads"][n]) <= 2e-5, (case["name"], n)
+                ref = case["grads"][n]
+                # With the norm after the recurrence and the loss h.sum(), the sum over a normalised row is the
+                # constant sum(beta): every gradient upstream of the norm is exactly zero and the reference
+                # holds rounding noise (~1e-8) there.  Judge such tensors by absolute difference.
+                if float(ref.abs().max()) < 1e-6:
+                    assert float((p.grad - ref).abs().max()) <= 1e-6, (case["name"], n)
+                else:
+                    assert rel_err(p.grad, ref) <= 2e-5, (case["name"], n)
 
 
 def test_regression_artifact_through_oracle(regression_case):

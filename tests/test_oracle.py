@@ -67,3 +67,20 @@ def test_oracle_forward_matches_reference_cpu_op(op_cases):
         assert rel_err(c_last, c_ref) <= 1e-6, case["name"]
         n += 1
     assert n >= 5
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float64, 1e-12), (torch.float32, 1e-5)])
+def test_oracle_layer_norm_matches_reference(layer_norm_cases, dtype, tol):
+    """The C restatement of layer normalisation against the reference's nn.LayerNorm (float64 vectors):
+    output, input gradient, weight and bias gradients."""
+    from oracle import sru_oracle
+    for case in layer_norm_cases:
+        x = case["x"].to(dtype)
+        x2d = x.reshape(-1, case["n"])
+        y, mean, rstd = sru_oracle.layer_norm_forward(x2d, case["weight"].to(dtype), case["bias"].to(dtype), case["eps"])
+        dx, dg, db = sru_oracle.layer_norm_backward(case["dy"].to(dtype).reshape(-1, case["n"]), x2d, mean, rstd,
+                                                    case["weight"].to(dtype))
+        assert rel_err(y.view_as(case["y"]), case["y"]) <= tol, case["n"]
+        assert rel_err(dx.view_as(case["dx"]), case["dx"]) <= tol, case["n"]
+        assert rel_err(dg, case["dweight"]) <= tol, case["n"]
+        assert rel_err(db, case["dbias"]) <= tol, case["n"]
