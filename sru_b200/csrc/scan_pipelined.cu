@@ -561,7 +561,7 @@ static bool choose_tile(int64_t L, int64_t B, int64_t d, int dirs, int k, int sk
     int v, ntc;
     if (s == 2) {
         if (!backward) {
-            if (w >= 20) { v = 4; ntc = 64; }
+            if (w >= 20) { v = 4; ntc = (w >= 40 && w < 80) ? 128 : 64; }
             else if (w >= 10) { v = has_pad ? 2 : 4; ntc = has_pad ? 64 : 128; }
             else if (w >= 5) { v = 1; ntc = 64; }
             else { v = 1; ntc = 128; }
@@ -582,6 +582,7 @@ static bool choose_tile(int64_t L, int64_t B, int64_t d, int dirs, int k, int sk
     v = env_int(backward ? "SRU_B200_BWD_V" : "SRU_B200_FWD_V", v);
     if (v < vmin || v > vmax || (v & (v - 1))) return false;
     ntc = env_int("SRU_B200_SCAN_THREADS", ntc);
+    ntc = env_int(backward ? "SRU_B200_BWD_THREADS" : "SRU_B200_FWD_THREADS", ntc);
     if (ntc < 32 || ntc > 128 || ntc % 32) return false;
     // hidden width of the tile: largest divisor of d, multiple of the granule, <= v*ntc, and with a
     // U slab of at most 2048 bytes (256 eight-byte elements, the widest box the tensor map takes)
