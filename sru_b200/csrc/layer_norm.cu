@@ -338,15 +338,36 @@ ln_bwd_kernel(TI *__restrict__ dx, float *__restrict__ part, const TO *__restric
     for (int c = threadIdx.x; c < 2 * n; c += kLnThreads) out[c] = colsum[c];
 }
 
-// dgamma[c] / dbeta[c] = sum over CTAs (in order) of their column sums
-__global__ void ln_reduce_kernel(const float *__restrict__ part, int nparts, int n,
-                                 float *__restrict__ dgamma, float *__restrict__ dbeta) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= 2 * n) return;
-    float s = 0.f;
-    for (int p = 0; p < nparts; ++p) s += part[(size_t)p * 2 * n + c];
-    if (c < n) { if (dgamma) dgamma[c] = s; }
-    else if (dbeta) dbeta[c - n] = s;
+// dgamma[c] / dbeta[c] = sum over the CTAs' column sums.  A CTA of 256 threads owns 32 columns: thread (slice, column)
+// adds every 8th partial with four independent accumulators (the loads of a serial sum would each wait for the one
+// before: 444 partials took 35 us that way), then the eight slices are combined in a fixed order.
+__global__ void __launch_bounds__(256)
+ln_reduce_kernel(const float *__restrict__ part, int nparts, int n,
+                 float *__restrict__ dgamma, float *__restrict__ dbeta) {
+    __shared__ float sm[8][32];
+    const int cx = threadIdx.x & 31, slice = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + cx;
+    const size_t w = (size_t)2 * n;
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    if (c < 2 * n) {
+        int p = slice;
+        for (; p + 24 < nparts; p += 32) {
+            a0 += part[(size_t)p * w + c];
+            a1 += part[(size_t)(p + 8) * w + c];
+            a2 += part[(size_t)(p + 16) * w + c];
+            a3 += part[(size_t)(p + 24) * w + c];
+        }
+        for (; p < nparts; p += 8) a0 += part[(size_t)p * w + c];
+    }
+    sm[slice][cx] = (a0 + a1) + (a2 + a3);
+    __syncthreads();
+    if (slice == 0 && c < 2 * n) {
+        float s = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) s += sm[k][cx];
+        if (c < n) { if (dgamma) dgamma[c] = s; }
+        else if (dbeta) dbeta[c - n] = s;
+    }
 }
 
 int sm_count() {
@@ -501,8 +522,7 @@ int sru_b200_layer_norm_backward(void *dx, float *dgamma, float *dbeta, const vo
     else rc = ln_backward_t<__half, __half>(dx, workspace, workspace_bytes, dy, x, mean, rstd, gamma, rows, ni, wpr, &nparts, st);
     if (rc) return rc;
     if (dgamma || dbeta) {
-        const int threads = 128;
-        ln_reduce_kernel<<<(2 * ni + threads - 1) / threads, threads, 0, st>>>(static_cast<const float *>(workspace), nparts, ni, dgamma, dbeta);
+        ln_reduce_kernel<<<(2 * ni + 31) / 32, 256, 0, st>>>(static_cast<const float *>(workspace), nparts, ni, dgamma, dbeta);
         SRUB_CUDA_CHECK(cudaGetLastError());
     }
     return 0;

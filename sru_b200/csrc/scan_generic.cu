@@ -161,28 +161,48 @@ __global__ void __launch_bounds__(128) scan_bwd_generic(ScanArgs a) {
     ((CT *)a.grad_init)[col] = cur;
 }
 
-// out[g][dj] = sum over row tiles r (in order) of part[r][g][dj]
+// out[g][dj] = sum over row tiles r of part[r][g][dj].  A CTA of 256 threads owns 32 columns: thread (slice, column)
+// adds every 8th tile with four independent accumulators (a serial sum waits for each load in turn), then the
+// eight slices are combined in a fixed order: deterministic for a given tile count.
 template <typename CT>
-__global__ void reduce_partials(const CT *__restrict__ part, CT *__restrict__ grad_wc,
-                                CT *__restrict__ grad_bias, int64_t ntiles, int64_t D, int write_wc) {
-    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // over 4*D
-    if (i >= 4 * D) return;
-    CT s = 0;
-    for (int64_t r = 0; r < ntiles; ++r) s += part[r * 4 * D + i];
-    if (i < 2 * D) {
-        if (write_wc) grad_wc[i] = s;
-    } else {
-        grad_bias[i - 2 * D] = s;
+__global__ void __launch_bounds__(256)
+reduce_partials(const CT *__restrict__ part, CT *__restrict__ grad_wc,
+                CT *__restrict__ grad_bias, int64_t ntiles, int64_t D, int write_wc) {
+    __shared__ CT sm[8][32];
+    const int cx = threadIdx.x & 31, slice = threadIdx.x >> 5;
+    const int64_t i = (int64_t)blockIdx.x * 32 + cx;  // over 4*D
+    const int64_t w = 4 * D;
+    CT a0 = 0, a1 = 0, a2 = 0, a3 = 0;
+    if (i < w) {
+        int64_t r = slice;
+        for (; r + 24 < ntiles; r += 32) {
+            a0 += part[r * w + i];
+            a1 += part[(r + 8) * w + i];
+            a2 += part[(r + 16) * w + i];
+            a3 += part[(r + 24) * w + i];
+        }
+        for (; r < ntiles; r += 8) a0 += part[r * w + i];
+    }
+    sm[slice][cx] = (a0 + a1) + (a2 + a3);
+    __syncthreads();
+    if (slice == 0 && i < w) {
+        CT s = 0;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) s += sm[k][cx];
+        if (i < 2 * D) {
+            if (write_wc) grad_wc[i] = s;
+        } else {
+            grad_bias[i - 2 * D] = s;
+        }
     }
 }
 
 template <typename CT>
 int launch_reduce_partials(const void *part, void *grad_wc, void *grad_bias, int64_t ntiles,
                            int64_t D, int write_wc, cudaStream_t st) {
-    const int threads = 128;
-    const int64_t blocks = (4 * D + threads - 1) / threads;
-    reduce_partials<CT><<<(unsigned)blocks, threads, 0, st>>>((const CT *)part, (CT *)grad_wc,
-                                                             (CT *)grad_bias, ntiles, D, write_wc);
+    const int64_t blocks = (4 * D + 31) / 32;
+    reduce_partials<CT><<<(unsigned)blocks, 256, 0, st>>>((const CT *)part, (CT *)grad_wc,
+                                                         (CT *)grad_bias, ntiles, D, write_wc);
     SRUB_CUDA_CHECK(cudaGetLastError());
     return 0;
 }
