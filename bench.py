@@ -253,6 +253,8 @@ def main():
     ap.add_argument("--config", type=int, default=5, choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cuda-graph", action="store_true",
+                    help="capture the step in one CUDA graph and time its replays (1 GPU; for launch-bound configs)")
     ap.add_argument("--cpu-sample-batch", type=int, default=0)
     ap.add_argument("--batch", type=int, default=0,
                     help="override the global batch (profiling on a small case; the workload name says so)")
@@ -343,6 +345,26 @@ def main():
         run_step(model, cfg, x_dev, mask_dev, c0, tokens_global, reducer)
     barrier()
 
+    # ---- optional: the whole step as one CUDA graph (the launchers are capture-safe) ----
+    graph = None
+    graph_out = None
+    graph_launches = 0
+    if args.cuda_graph and world == 1:
+        n0 = _lib.launch_count
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            graph_out = run_step(model, cfg, x_dev, mask_dev, c0, tokens_global, None)
+        graph_launches = _lib.launch_count - n0
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+
+    def step_resident():
+        if graph is not None:
+            graph.replay()
+            return graph_out
+        return run_step(model, cfg, x_dev, mask_dev, c0, tokens_global, reducer)
+
     # ---- timed: device-resident inputs ----
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
@@ -352,11 +374,13 @@ def main():
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        run_step(model, cfg, x_dev, mask_dev, c0, tokens_global, reducer)
+        step_resident()
     e1.record()
     barrier()
     ms_total = max_over_ranks(e0.elapsed_time(e1))
     launches = _lib.launch_count - launches0          # this rank's own kernels inside the timed region
+    if graph is not None:
+        launches = graph_launches * args.steps        # kernel nodes of the graph, replayed
     clocks = sampler.stop() if sampler else None
     ms_per_step = ms_total / args.steps
     value = tokens_global / (ms_per_step / 1e3)
@@ -366,9 +390,15 @@ def main():
     e0.record()
     result_bytes = 0
     for _ in range(args.steps):
-        xd = x_pin.to(device, non_blocking=True)
-        md = None if mask_pin is None else mask_pin.to(device, non_blocking=True)
-        out = run_step(model, cfg, xd, md, c0, tokens_global, reducer)
+        if graph is not None:
+            x_dev.copy_(x_pin, non_blocking=True)         # the graph reads its inputs from these buffers
+            if mask_pin is not None:
+                mask_dev.copy_(mask_pin, non_blocking=True)
+            out = step_resident()
+        else:
+            xd = x_pin.to(device, non_blocking=True)
+            md = None if mask_pin is None else mask_pin.to(device, non_blocking=True)
+            out = run_step(model, cfg, xd, md, c0, tokens_global, reducer)
         host = out.float().cpu()
         result_bytes = host.numel() * host.element_size()
     e1.record()
@@ -446,7 +476,8 @@ def main():
         "data": "synthetic",
         "config": {"workload": cfg["name"], "global_batch": cfg["B"], "seq_len": cfg["L"],
                    "parallelism": "batch-sharded dp%d" % world, "l2": "inputs larger than L2",
-                   "gemm": gemm_backend(), "c_hist": ops._c_hist_dtype, "amp_mode": ops.get_amp_mode()},
+                   "gemm": gemm_backend(), "c_hist": ops._c_hist_dtype, "amp_mode": ops.get_amp_mode(),
+                   "cuda_graph": graph is not None},
         "e2e": {"value": tokens_global / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": result_bytes},
         "gpu_launches": launches,

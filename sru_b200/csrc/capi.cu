@@ -33,6 +33,26 @@ int *device_error_flag() {
     return cache[dev];
 }
 
+// Driver entry points (the tensor-map encoder) need the device's primary context current on the calling
+// thread.  A thread that has only inherited a device ordinal (an autograd worker, for instance) gets it
+// bound by a no-op runtime call; a thread that already has a context makes no runtime call at all, so that
+// the launchers stay legal inside a stream capture.
+int ensure_context() {
+    typedef CUresult (*GetCurrent)(CUcontext *);
+    static GetCurrent get_current = nullptr;
+    if (!get_current) {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuCtxGetCurrent", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            get_current = reinterpret_cast<GetCurrent>(ptr);
+    }
+    CUcontext ctx = nullptr;
+    if (get_current && get_current(&ctx) == CUDA_SUCCESS && ctx != nullptr) return 0;
+    SRUB_CUDA_CHECK(cudaFree(nullptr));
+    return 0;
+}
+
 static int check_common(int64_t L, int64_t B, int64_t d, int dirs, int k, int act, int skip,
                         int dtype, int c_dtype) {
     if (L < 0 || B < 0 || d < 1) return set_error(SRU_ERR_BAD_ARG, "bad sizes L=%lld B=%lld d=%lld",

@@ -17,6 +17,7 @@ namespace srub {
 // ---------------------------------------------------------------------------------------
 int set_error(int code, const char *fmt, ...);
 int *device_error_flag();  // device int, set non-zero by a kernel whose bounded wait gave up
+int ensure_context();      // binds the device's primary context to this thread if it has none; 0 or SRU_ERR_CUDA
 
 #define SRUB_CUDA_CHECK(expr)                                                              \
     do {                                                                                   \

@@ -699,10 +699,8 @@ static int gemm_impl(void *c, const void *a, const void *b, const float *col_bia
         return set_error(SRU_ERR_BAD_ARG, "gemm leading dimensions and N must be multiples of 8 elements");
     if (m > 0x7fffffff || n > 0x7fffffff || k_dim > 0x7fffffff) return set_error(SRU_ERR_BAD_ARG, "gemm size too large");
 
-    // The tensor-map encoder is a driver entry point and needs the device's primary context
-    // current on THIS thread; a thread that has only inherited a device ordinal (an autograd
-    // worker, for instance) gets it bound by this no-op runtime call.
-    SRUB_CUDA_CHECK(cudaFree(nullptr));
+    // the tensor-map encoder is a driver entry point: this thread needs the primary context
+    if (int rc = ensure_context()) return rc;
 
     // Pair kernel (two SMs per 256 x 256 tile) once there are enough such tiles to fill the GPU;
     // SRU_B200_GEMM_2SM=0/1 overrides.  Split-K needs a caller workspace; without one it is off.

@@ -698,8 +698,8 @@ int launch_scan_pipelined(const ScanArgs &a, bool backward, cudaStream_t st) {
     if (!choose_tile(a.L, a.B, a.d, a.dirs, a.k, a.skip_type, a.dtype, a.c_dtype, backward, a.mask_pad != nullptr, &p.c)) return 0;
     p.err = err;
 
-    // The tensor-map encoder is a driver entry point: make sure this thread has the primary context.
-    SRUB_CUDA_CHECK(cudaFree(nullptr));
+    // the tensor-map encoder is a driver entry point: this thread needs the primary context
+    if (int rc = ensure_context()) return rc;
     const int64_t s = (int64_t)dtype_size(a.dtype), sc = (int64_t)dtype_size(a.c_dtype);
     const int64_t D = (int64_t)a.d * a.dirs;
     ScanMaps maps;

@@ -147,6 +147,23 @@ def _prep_small(t: Optional[Tensor], dtype: torch.dtype) -> Optional[Tensor]:
     return t.detach().to(dtype).contiguous()
 
 
+def _scale_value(scale_x: Optional[Tensor]) -> float:
+    """The scalar the kernels take for ``scale_x`` (sru/cuda_functional.py:73-78).  Reading a device tensor
+    synchronises the stream, so the value is remembered on the tensor object together with the tensor's
+    version counter and read again only after an in-place change (load_state_dict, reset_parameters)."""
+    if scale_x is None:
+        return 1.0
+    cached = getattr(scale_x, "_sru_b200_scalar", None)
+    if cached is not None and cached[0] == scale_x._version:
+        return cached[1]
+    value = float(scale_x.reshape(-1)[0])
+    try:
+        scale_x._sru_b200_scalar = (scale_x._version, value)
+    except Exception:       # tensors that refuse attributes are simply read every time
+        pass
+    return value
+
+
 class ElementwiseRecurrence(Function):
     """Autograd function of the scan; argument order of sru/cuda_functional.py:158-169."""
 
@@ -165,7 +182,7 @@ class ElementwiseRecurrence(Function):
         init_c = _prep_small(init, sm)
         mask_c_c = _prep_small(mask_c, sm)
         pad_c = mask_pad.bool().contiguous() if mask_pad is not None else None
-        scale = 1.0 if scale_x is None else float(scale_x.reshape(-1)[0])
+        scale = _scale_value(scale_x)
         need_hist = any(ctx.needs_input_grad[:5])
         h, c_hist, c_last = scan_forward(u_c.view(length, batch, D * k), x_c, wc_c, bias_c, init_c,
                                          mask_c_c, pad_c, length, batch, d_out, dirs, k,
@@ -217,7 +234,7 @@ def elementwise_recurrence_forward(u: Tensor, x: Tensor, weight_c: Tensor, bias:
     st = u.dtype
     sm = _small_dtype(st)
     D = d_out * dirs
-    scale = 1.0 if scale_x is None else float(scale_x.reshape(-1)[0])
+    scale = _scale_value(scale_x)
     h, c_hist, c_last = scan_forward(
         u.detach().contiguous().view(length, batch, D * k),
         x.detach().to(st).contiguous() if skip_type == 1 else None,
@@ -270,7 +287,7 @@ def _forward_nograd(U, x, weight_c, bias, c_init, activation_type, hidden_size, 
     st = U.dtype
     sm = _small_dtype(st)
     D = hidden_size * dirs
-    scale = 1.0 if scale_x is None else float(scale_x.reshape(-1)[0])
+    scale = _scale_value(scale_x)
     h, _, c_last = scan_forward(
         U.detach().contiguous().view(length, batch, D * k),
         x.detach().to(st).contiguous() if skip_type == 1 else None,
