@@ -60,8 +60,43 @@ struct GemmArgs {
     uint32_t idesc;
     int tiles_m, tiles_n;
     int ksplit, kbps;   // split-K: partial products over kbps k-blocks each go to slab sp of an fp32 workspace
+    // Tail split (pair kernel): tiles [0, tail_t0) are whole rounds of the persistent grid and are computed in one
+    // piece; each of the remaining tiles is cut into tail_s K slabs of tail_kbps k-blocks whose fp32 256 x 256
+    // partials go to tail_ws[(tile - tail_t0) * tail_s + slab]; tail_reduce finishes them.  tail_s == 0: off.
+    int tail_t0, tail_s, tail_kbps;
+    float *tail_ws;
     int *err;
 };
+
+// One work unit of the persistent loop: a tile (or a K slab of one) and where its result goes.
+struct GemmUnit {
+    int tile, kb0, kb1;
+    int sp;      // slab index of a uniform split (result row offset sp * M in the workspace)
+    int slot;    // >= 0: tail split, partial tile number `slot` of tail_ws; -1 otherwise
+};
+__device__ __forceinline__ GemmUnit decode_unit(const GemmArgs &g, int unit, int nkb) {
+    GemmUnit u;
+    if (g.tail_s > 0) {
+        u.sp = 0;
+        if (unit < g.tail_t0) {
+            u.tile = unit; u.kb0 = 0; u.kb1 = nkb; u.slot = -1;
+        } else {
+            const int v = unit - g.tail_t0;
+            const int tt = v / g.tail_s, slab = v - tt * g.tail_s;
+            u.tile = g.tail_t0 + tt;
+            u.kb0 = slab * g.tail_kbps;
+            u.kb1 = min(nkb, u.kb0 + g.tail_kbps);
+            u.slot = v;
+        }
+    } else {
+        u.tile = unit / g.ksplit;
+        u.sp = unit - u.tile * g.ksplit;
+        u.kb0 = u.sp * g.kbps;
+        u.kb1 = min(nkb, u.kb0 + g.kbps);
+        u.slot = -1;
+    }
+    return u;
+}
 
 // ---- PTX wrappers -----------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y) {
@@ -453,7 +488,9 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();               // 0 = leader
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
-    const int nunits = g.tiles_m * g.tiles_n * g.ksplit;   // work units: (256 x 256 tile, k-split)
+    const int ntiles_all = g.tiles_m * g.tiles_n;
+    // work units: (256 x 256 tile, K slab)
+    const int nunits = g.tail_s > 0 ? g.tail_t0 + (ntiles_all - g.tail_t0) * g.tail_s : ntiles_all * g.ksplit;
     const int nkb = (int)((g.K + BK - 1) / BK);
 
     if (threadIdx.x == 0) {
@@ -478,9 +515,9 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             uint32_t phase = 0;
             bool ok = true;
             for (int unit = pair; unit < nunits && ok; unit += npairs) {
-                const int tile = unit / g.ksplit, sp = unit - tile * g.ksplit;
-                const int kb0 = sp * g.kbps, kb1 = min(nkb, kb0 + g.kbps);
-                const int mb = tile / g.tiles_n, nb = tile % g.tiles_n;
+                const GemmUnit u = decode_unit(g, unit, nkb);
+                const int kb0 = u.kb0, kb1 = u.kb1;
+                const int mb = u.tile / g.tiles_n, nb = u.tile % g.tiles_n;
                 const int m0 = mb * 256 + (int)rank * 128;      // this CTA's rows of A
                 const int n0 = nb * BN + (int)rank * 128;       // this CTA's columns of B
                 for (int kb = kb0; kb < kb1; ++kb) {
@@ -516,8 +553,8 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             const uint32_t a_step = g.a_mn ? 2048u : 32u, b_step = g.b_mn ? 2048u : 32u;
             const uint32_t a_lbo = g.a_mn ? 8192u : 16u, b_lbo = g.b_mn ? 8192u : 16u;
             for (int unit = pair; unit < nunits && ok; unit += npairs, ++it) {
-                const int tile = unit / g.ksplit, sp = unit - tile * g.ksplit;
-                const int kb0 = sp * g.kbps, kb1 = min(nkb, kb0 + g.kbps);
+                const GemmUnit u = decode_unit(g, unit, nkb);
+                const int kb0 = u.kb0, kb1 = u.kb1;
                 const int acc = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1;
                 if (!mbar_wait_bounded(bar_tempty + 8 * acc, acc_phase ^ 1)) { atomicExch(g.err, 22); break; }
@@ -547,9 +584,9 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         uint8_t *stg = smem + kStages2 * (kAStage2 + kBStage2) + 256 + q * kStgWarp;
         int it = 0;
         for (int unit = pair; unit < nunits; unit += npairs, ++it) {
-                const int tile = unit / g.ksplit, sp = unit - tile * g.ksplit;
-                const int kb0 = sp * g.kbps, kb1 = min(nkb, kb0 + g.kbps);
-            const int mb = tile / g.tiles_n, nb = tile % g.tiles_n;
+            const GemmUnit u = decode_unit(g, unit, nkb);
+            const int sp = u.sp;
+            const int mb = u.tile / g.tiles_n, nb = u.tile % g.tiles_n;
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
             if (!mbar_wait_bounded(bar_tfull + 8 * acc, acc_phase)) { if (lane == 0) atomicExch(g.err, 24); break; }
@@ -558,7 +595,20 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             const int64_t row = row0 + lane;
             const int64_t col_base = (int64_t)nb * BN;
             const uint32_t tmem_warp = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
-            if (g.c_dtype == SRU_BF16) {
+            if (u.slot >= 0) {
+                // a K slab of a tail tile: the raw fp32 accumulators, tile-local [256][256]
+                GemmArgs gp = g;
+                gp.c = g.tail_ws + (size_t)u.slot * 65536;
+                gp.ldc = 256; gp.N = 256; gp.bias = nullptr; gp.accumulate = 0;
+                const int64_t lrow = (int64_t)rank * 128 + q * 32 + lane;
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld32(tmem_warp + c * 32, r);
+                    tmem_ld_wait();
+                    epilogue_chunk<float>(gp, r, lrow, c * 32);
+                }
+            } else if (g.c_dtype == SRU_BF16) {
                 epilogue_staged<__nv_bfloat16>(g, tmem_warp, row0, col_base, stg, lane);
             } else if (g.c_dtype == SRU_F16) {
                 epilogue_staged<__half>(g, tmem_warp, row0, col_base, stg, lane);
@@ -609,6 +659,57 @@ __global__ void splitk_reduce(const float *__restrict__ ws, int nsplit, int64_t 
         o[0] = Cvt<TO>::from_f(acc.x); o[1] = Cvt<TO>::from_f(acc.y);
         o[2] = Cvt<TO>::from_f(acc.z); o[3] = Cvt<TO>::from_f(acc.w);
     }
+}
+
+// Tail-split finish: tile t0 + tt of C = sum over its K slabs of the fp32 partial tiles (+ C when accumulating).
+template <typename TO>
+__global__ void tail_reduce(const float *__restrict__ ws, int nslab, int t0, int tiles_n, int64_t M, int64_t N,
+                            TO *__restrict__ c, int64_t ldc, int accumulate) {
+    const int tt = blockIdx.x >> 6;                                  // 64 blocks of 256 threads x 4 columns per tile
+    const int e = ((blockIdx.x & 63) * 256 + threadIdx.x) * 4;      // element of the 256 x 256 tile
+    const int r = e >> 8, col = e & 255;
+    const int tile = t0 + tt;
+    const int64_t row = (int64_t)(tile / tiles_n) * 256 + r, gcol = (int64_t)(tile % tiles_n) * 256 + col;
+    if (row >= M || gcol >= N) return;                               // N is a multiple of 8
+    const float *p = ws + (size_t)tt * nslab * 65536 + e;
+    float4 acc = *reinterpret_cast<const float4 *>(p);
+    for (int sp = 1; sp < nslab; ++sp) {
+        const float4 v = *reinterpret_cast<const float4 *>(p + (size_t)sp * 65536);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    TO *o = c + row * ldc + gcol;
+    if (accumulate) {
+        acc.x += Cvt<TO>::to_f(o[0]); acc.y += Cvt<TO>::to_f(o[1]);
+        acc.z += Cvt<TO>::to_f(o[2]); acc.w += Cvt<TO>::to_f(o[3]);
+    }
+    o[0] = Cvt<TO>::from_f(acc.x); o[1] = Cvt<TO>::from_f(acc.y);
+    o[2] = Cvt<TO>::from_f(acc.z); o[3] = Cvt<TO>::from_f(acc.w);
+}
+
+// Tail split of a product on the pair kernel.  The persistent grid of `workers` CTA pairs walks the tiles in
+// rounds; with R whole rounds and r tiles left, the last round keeps only r of the workers busy.  Cutting each of
+// the r tiles into S slabs makes ceil(r*S/workers) short rounds of 1/S length instead.  Worth it only when the
+// product has few rounds (a weight gradient: 192 tiles on 74 pairs is 2.6 rounds of work done in 3).
+// OFF unless SRU_B200_GEMM_TAIL=1: measured on B200 it does not pay.  These products run at the board's power
+// limit, where time follows energy; while only 44 of 74 pairs work in the last round the clocks rise, and the
+// product takes the same 4.8 ms with and without the split (and the whole training step the same 215 ms).
+// Returns S (0: no tail split) and the number of whole-round tiles in *t0.
+int choose_tail_split(int64_t tiles, int workers, int nkb, int *t0) {
+    *t0 = 0;
+    const char *e = getenv("SRU_B200_GEMM_TAIL");
+    if (!e || atoi(e) == 0) return 0;
+    const int64_t rounds = tiles / workers, r = tiles % workers;
+    if (rounds < 1 || rounds > 6 || r == 0 || nkb < 128) return 0;
+    int best = 0;
+    double best_len = 1.0;     // length of the last round without a split
+    for (int sp = 2; sp <= 8; ++sp) {
+        if (nkb / sp < 32) break;
+        const double len = (double)((r * sp + workers - 1) / workers) / sp;
+        if (len < best_len - 0.04) { best_len = len; best = sp; }
+    }
+    if (best == 0 || best_len > 0.85) return 0;
+    *t0 = (int)(rounds * workers);
+    return best;
 }
 
 // How many K slabs to cut a product into: only when the tiles alone leave the last wave of the
@@ -667,7 +768,8 @@ int make_map(CUtensorMap *map, const void *base, int dtype, int64_t inner, int64
 using namespace srub;
 
 // Kernel choice for a problem: pair kernel or single-CTA kernel, and the number of K slabs.
-static int gemm_plan(int64_t m, int64_t n, int64_t k_dim, bool has_bias, bool *two_sm, int *ksplit) {
+static int gemm_plan(int64_t m, int64_t n, int64_t k_dim, bool has_bias, bool *two_sm, int *ksplit,
+                     int *tail_s, int *tail_t0) {
     int dev = 0, sms = 148;
     SRUB_CUDA_CHECK(cudaGetDevice(&dev));
     SRUB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
@@ -678,6 +780,9 @@ static int gemm_plan(int64_t m, int64_t n, int64_t k_dim, bool has_bias, bool *t
     const int nkb = (int)((k_dim + BK - 1) / BK);
     *two_sm = pair;
     *ksplit = has_bias ? 1 : choose_ksplit(tiles, pair ? sms / 2 : sms, nkb);
+    *tail_s = 0;
+    *tail_t0 = 0;
+    if (pair && !has_bias && *ksplit == 1) *tail_s = choose_tail_split(tiles, sms / 2, nkb, tail_t0);
     return 0;
 }
 
@@ -708,8 +813,8 @@ static int gemm_impl(void *c, const void *a, const void *b, const float *col_bia
     SRUB_CUDA_CHECK(cudaGetDevice(&dev));
     SRUB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     bool two_sm = false;
-    int ksplit = 1;
-    if (int prc = gemm_plan(m, n, k_dim, col_bias != nullptr, &two_sm, &ksplit)) return prc;
+    int ksplit = 1, tail_s = 0, tail_t0 = 0;
+    if (int prc = gemm_plan(m, n, k_dim, col_bias != nullptr, &two_sm, &ksplit, &tail_s, &tail_t0)) return prc;
     const int nkb_all = (int)((k_dim + BK - 1) / BK);
     int kbps = (nkb_all + ksplit - 1) / ksplit;
     ksplit = (nkb_all + kbps - 1) / kbps;
@@ -748,12 +853,23 @@ static int gemm_impl(void *c, const void *a, const void *b, const float *col_bia
     if (!g.err) return set_error(SRU_ERR_CUDA, "device error flag unavailable");
     g.ksplit = ksplit;
     g.kbps = kbps;
+    g.tail_s = 0; g.tail_t0 = 0; g.tail_kbps = 0; g.tail_ws = nullptr;
+    const int64_t tiles_all = (int64_t)g.tiles_m * g.tiles_n;
+    if (tail_s > 0) {
+        const size_t need = (size_t)(tiles_all - tail_t0) * tail_s * 65536 * sizeof(float);
+        if (workspace && workspace_bytes >= need) {
+            g.tail_s = tail_s; g.tail_t0 = tail_t0;
+            g.tail_kbps = (nkb_all + tail_s - 1) / tail_s;
+            g.tail_ws = static_cast<float *>(workspace);
+        }
+    }
     void *final_c = c;
     const int final_dtype = c_dtype, final_acc = g.accumulate;
     if (ksplit > 1) {   // partial products go to [ksplit][M][N] fp32; splitk_reduce finishes the job
         g.c = workspace; g.ldc = n; g.c_dtype = SRU_F32; g.accumulate = 0;
     }
-    const int64_t ntiles = (int64_t)g.tiles_m * g.tiles_n * ksplit;   // work units
+    const int64_t ntiles = g.tail_s > 0 ? g.tail_t0 + (tiles_all - g.tail_t0) * g.tail_s
+                                        : tiles_all * ksplit;   // work units
     if (ntiles > 0x7fffffff) return set_error(SRU_ERR_BAD_ARG, "too many gemm tiles");
 
     static bool attr_set[64] = {false};
@@ -782,6 +898,17 @@ static int gemm_impl(void *c, const void *a, const void *b, const float *col_bia
         gemm_tcgen05_kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(map_a, map_b, g);
     }
     SRUB_CUDA_CHECK(cudaGetLastError());
+    if (g.tail_s > 0) {
+        const unsigned blocks = (unsigned)((tiles_all - g.tail_t0) * 64);
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        if (final_dtype == SRU_BF16)
+            tail_reduce<__nv_bfloat16><<<blocks, 256, 0, st>>>(g.tail_ws, g.tail_s, g.tail_t0, g.tiles_n, m, n, (__nv_bfloat16 *)final_c, ldc, final_acc);
+        else if (final_dtype == SRU_F16)
+            tail_reduce<__half><<<blocks, 256, 0, st>>>(g.tail_ws, g.tail_s, g.tail_t0, g.tiles_n, m, n, (__half *)final_c, ldc, final_acc);
+        else
+            tail_reduce<float><<<blocks, 256, 0, st>>>(g.tail_ws, g.tail_s, g.tail_t0, g.tiles_n, m, n, (float *)final_c, ldc, final_acc);
+        SRUB_CUDA_CHECK(cudaGetLastError());
+    }
     if (ksplit > 1) {
         const int64_t items = m * (n / 4);
         const unsigned blocks = (unsigned)std::min<int64_t>((items + 255) / 256, (int64_t)sms * 8);
@@ -808,8 +935,13 @@ extern "C" int sru_b200_gemm(void *c, const void *a, const void *b, const float 
 extern "C" size_t sru_b200_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k_dim, int has_bias) {
     if (m <= 0 || n <= 0 || k_dim <= 0) return 0;
     bool two_sm = false;
-    int ksplit = 1;
-    if (gemm_plan(m, n, k_dim, has_bias != 0, &two_sm, &ksplit) != 0 || ksplit <= 1) return 0;
+    int ksplit = 1, tail_s = 0, tail_t0 = 0;
+    if (gemm_plan(m, n, k_dim, has_bias != 0, &two_sm, &ksplit, &tail_s, &tail_t0) != 0) return 0;
+    if (tail_s > 0) {
+        const int64_t tiles = ((m + 255) / 256) * ((n + BN - 1) / BN);
+        return (size_t)(tiles - tail_t0) * tail_s * 65536 * sizeof(float);
+    }
+    if (ksplit <= 1) return 0;
     return (size_t)ksplit * (size_t)m * (size_t)n * sizeof(float);
 }
 

@@ -137,3 +137,35 @@ def test_gemm_split_k(force):
     finally:
         os.environ.pop("SRU_B200_GEMM_KSPLIT", None)
     assert rel_err(out, ref) <= 1e-4 and rel_err(out16, ref) <= 1e-2 and rel_err(acc, ref + base) <= 1e-4
+
+
+@pytest.mark.parametrize("mn", [(2048, 6144), (2000, 6136)])
+def test_gemm_tail_split(mn):
+    """A product with few rounds of tiles on the persistent grid (192 tiles of 256 x 256 on 74 CTA pairs): the tiles
+    of the last, partly filled round are cut into K slabs (fp32 partial tiles in the caller's workspace, summed by a
+    second kernel).  Same product as without the split, also for ragged edges, fp32 output and accumulation."""
+    import os
+    from sru_b200 import _lib
+    gemm = _gemm()
+    M, N = mn
+    K = 8192
+    g = torch.Generator().manual_seed(33)
+    a = (torch.randn(K, M, generator=g) * 0.1).bfloat16().to(DEV)     # weight-gradient layout: x^T grad_U
+    b = (torch.randn(K, N, generator=g) * 0.1).bfloat16().to(DEV)
+    ref = a.float().t() @ b.float()
+    assert _lib.lib().sru_b200_gemm_workspace_bytes(M, N, K, 0) == 0          # the split is opt-in
+    plain32 = gemm(a, b, trans_a=True, out_dtype=torch.float32)
+    os.environ["SRU_B200_GEMM_TAIL"] = "1"
+    try:
+        assert _lib.lib().sru_b200_gemm_workspace_bytes(M, N, K, 0) > 0
+        out32 = gemm(a, b, trans_a=True, out_dtype=torch.float32)
+        out16 = gemm(a, b, trans_a=True)
+        base = torch.randn(M, N, generator=g).to(DEV)
+        acc = base.clone()
+        gemm(a, b, trans_a=True, out=acc, accumulate=True)
+    finally:
+        os.environ.pop("SRU_B200_GEMM_TAIL", None)
+    torch.cuda.synchronize()
+    _lib.check_device_error()
+    assert rel_err(out32, ref) <= 1e-4 and rel_err(out16, ref) <= 1e-2 and rel_err(acc, ref + base) <= 1e-4
+    assert rel_err(out32, plain32) <= 1e-5
