@@ -774,7 +774,8 @@ static int gemm_plan(int64_t m, int64_t n, int64_t k_dim, bool has_bias, bool *t
     SRUB_CUDA_CHECK(cudaGetDevice(&dev));
     SRUB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     const int64_t tiles256 = ((m + 255) / 256) * ((n + BN - 1) / BN);
-    bool pair = tiles256 >= sms / 2;
+    // measured: from about 32 tiles of 256 x 256 on, the pair kernel beats twice as many 128 x 256 tiles on single CTAs
+    bool pair = tiles256 >= 32;
     if (const char *e = getenv("SRU_B200_GEMM_2SM")) pair = (*e == '1');
     const int64_t tiles = pair ? tiles256 : ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
     const int nkb = (int)((k_dim + BK - 1) / BK);

@@ -236,6 +236,44 @@ def test_pad_flags_across_stages(v, threads, ss):
         compare(out, ref, TOL[torch.float32], (v, threads, ss, pad, "fp32"))
 
 
+def test_edge_cases_empty_single_and_fully_padded():
+    """Zero-length and zero-batch calls return empty outputs and pass the initial state through; one step and one
+    sequence work; a sequence that is padding from the first step keeps c_init, gives h = 0 and passes grad_last
+    through to grad_init."""
+    ops = _ops()
+    dev = "cuda:0"
+    d, dirs, k = 64, 2, 3
+    D = d * dirs
+    g = torch.Generator().manual_seed(77)
+    wc, bias = torch.randn(2 * D, generator=g).to(dev), torch.randn(2 * D, generator=g).to(dev)
+    for (L, B) in ((0, 3), (4, 0)):
+        U = torch.empty(L, B, D * k, device=dev, dtype=torch.bfloat16)
+        x = torch.empty(L, B, D, device=dev, dtype=torch.bfloat16)
+        c0 = torch.randn(B, D, generator=g).to(dev)
+        h, ch, cl = ops.scan_forward(U, x, wc, bias, c0, None, None, L, B, d, dirs, k, 0, 1, 0, 1.0)
+        assert h.shape == (L, B, D) and ch.shape == (L, B, D) and torch.equal(cl, c0)
+        gl = torch.randn(B, D, generator=g).to(dev)
+        gu, gx, gwc, gb, gi = ops.scan_backward(U, x, wc, bias, c0, None, None, ch, torch.empty_like(x), gl,
+                                                L, B, d, dirs, k, 0, 1, 0, 1.0)
+        assert gu.shape == U.shape and float(gwc.abs().sum()) == 0.0 and torch.equal(gi, gl)
+    for (L, B) in ((1, 1), (1, 5), (6, 1)):
+        inp = random_inputs(L, B, d, dirs, k, pad=None, seed=L * 10 + B)
+        out, ref = run_both(inp, torch.bfloat16)
+        compare(out, ref, TOL[torch.bfloat16], ("single", L, B))
+    # sequence 1 of 3 is padding everywhere
+    L, B = 12, 3
+    inp = list(random_inputs(L, B, d, dirs, k, pad="tail", seed=5))
+    mp = inp[6].clone()
+    mp[:, 1] = True
+    inp[6] = mp
+    out, ref = run_both(tuple(inp), torch.float32)
+    compare(out, ref, TOL[torch.float32], "fully padded")
+    c0, gl = inp[4], inp[8]
+    assert float(out["h"][:, 1].abs().max()) == 0.0
+    assert torch.equal(out["c_last"][1].cpu(), c0[1]) and torch.equal(out["grad_init"][1].cpu(), gl[1])
+    assert float(out["grad_u"].view(L, B, -1)[:, 1].abs().max()) == 0.0
+
+
 def test_options_no_skip_no_bias_no_c0():
     ops = _ops()
     inp = list(random_inputs(10, 4, 64, 2, 3, skip=0, pad="tail", maskc=False, c0=False, seed=5))
