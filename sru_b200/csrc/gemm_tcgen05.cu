@@ -34,6 +34,7 @@
 #include <cudaTypedefs.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 
@@ -65,7 +66,84 @@ struct GemmArgs {
     // partials go to tail_ws[(tile - tail_t0) * tail_s + slab]; tail_reduce finishes them.  tail_s == 0: off.
     int tail_t0, tail_s, tail_kbps;
     float *tail_ws;
+    // Dynamic tile order (pair kernel): word 0 is the next-unit counter, then kSchedRing mailbox words per CTA pair.
+    // NULL: static order (unit = pair, pair + pairs, ...).
+    unsigned long long *sched;
     int *err;
+};
+
+// ---- dynamic tile order ---------------------------------------------------------------------------------
+// With a static order every CTA pair owns a fixed share of the tiles, so the product lasts as long as its slowest
+// pair: when another kernel (a gradient all-reduce running next to backward) holds a few SMs for a while, the pairs
+// on those SMs start late and everyone waits for them.  Here the leader CTA's producer thread takes the next unit
+// from a global counter and posts it to the pair's mailbox ring; the other roles of both CTAs (the peer's producer,
+// the MMA thread, the epilogue warps) read it there.  A mailbox word is (iteration << 32 | unit), so a stale word
+// never matches; the ring (16 words) cannot be overrun because the barriers of the pipeline already keep the roles
+// within a few tiles of each other (shared-memory stages, two accumulators) and the poster runs two units ahead.  The host fills counter and mailboxes with 0xFF bytes before the launch: the counter
+// then yields 0, 1, 2, ... as old value + 1, and no mailbox matches iteration 0.
+constexpr int kSchedRing = 16;
+constexpr int kSchedMaxPairs = 128;
+constexpr int kSchedWords = 1 + kSchedMaxPairs * kSchedRing;
+
+__device__ __forceinline__ unsigned int sched_take(const GemmArgs &g) {
+    return atomicAdd(reinterpret_cast<unsigned int *>(g.sched), 1u) + 1u;
+}
+__device__ __forceinline__ int sched_post(const GemmArgs &g, int pair, int it, unsigned int u, int nunits) {
+    const int unit = (u < (unsigned int)nunits) ? (int)u : -1;
+    const unsigned long long v = ((unsigned long long)(unsigned int)it << 32) | (unsigned int)unit;
+    unsigned long long *slot = g.sched + 1 + pair * kSchedRing + (it % kSchedRing);
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(slot), "l"(v) : "memory");   // the word is the whole message
+    return unit;
+}
+__device__ __forceinline__ int sched_post_next(const GemmArgs &g, int pair, int it, int nunits) {
+    const unsigned int u = atomicAdd(reinterpret_cast<unsigned int *>(g.sched), 1u) + 1u;
+    const int unit = (u < (unsigned int)nunits) ? (int)u : -1;
+    const unsigned long long v = ((unsigned long long)(unsigned int)it << 32) | (unsigned int)unit;
+    unsigned long long *slot = g.sched + 1 + pair * kSchedRing + (it % kSchedRing);
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(slot), "l"(v) : "memory");   // the word is the whole message
+    return unit;
+}
+// false in *ok: the word did not arrive within ~2 s (the caller raises the device error flag and leaves)
+__device__ __forceinline__ int sched_read(const GemmArgs &g, int pair, int it, bool *ok) {
+    const unsigned long long *slot = g.sched + 1 + pair * kSchedRing + (it % kSchedRing);
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i) {
+            unsigned long long v;
+            asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(slot) : "memory");
+            if ((unsigned int)(v >> 32) == (unsigned int)it) return (int)(unsigned int)v;
+            if (i > 8) __nanosleep(64);
+        }
+        if (global_timer_ns() - t0 > 2000000000ull) { *ok = false; return -1; }
+    }
+}
+// A role that reads its units from the mailbox.  The word of the NEXT iteration is requested while the current unit
+// is being worked on (the poster is two units ahead, so it is normally there), which keeps the global-memory
+// latency of the mailbox out of the per-tile critical path; only the value itself is communicated, so the
+// accesses are relaxed.  Without a mailbox (g.sched == NULL) the order is static: pair, pair + pairs, ...
+struct UnitReader {
+    unsigned long long next_word;
+    __device__ __forceinline__ static unsigned long long peek(const GemmArgs &g, int pair, int it) {
+        unsigned long long v;
+        const unsigned long long *slot = g.sched + 1 + pair * kSchedRing + (it % kSchedRing);
+        asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(slot) : "memory");
+        return v;
+    }
+    __device__ __forceinline__ void init(const GemmArgs &g, int pair) {
+        next_word = g.sched ? peek(g, pair, 0) : 0ull;
+    }
+    __device__ __forceinline__ int get(const GemmArgs &g, int pair, int npairs, int nunits, int it, bool *ok) {
+        if (!g.sched) {
+            const int unit = pair + it * npairs;
+            return unit < nunits ? unit : -1;
+        }
+        const unsigned long long w = next_word;
+        const int unit = ((unsigned int)(w >> 32) == (unsigned int)it) ? (int)(unsigned int)w
+                                                                       : sched_read(g, pair, it, ok);
+        if (*ok && unit >= 0) next_word = peek(g, pair, it + 1);
+        return unit;
+    }
 };
 
 // One work unit of the persistent loop: a tile (or a K slab of one) and where its result goes.
@@ -514,7 +592,27 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int unit = pair; unit < nunits && ok; unit += npairs) {
+            // The leader's producer posts units two iterations ahead: the counter's round trip and the time until
+            // the peer sees the mailbox stay behind a whole tile of loads.
+            const bool poster = g.sched != nullptr && rank == 0;
+            int ahead1 = -1;            // unit of iteration it + 1 (poster only)
+            int cur = -1;
+            if (poster) {
+                cur = sched_post_next(g, pair, 0, nunits);
+                ahead1 = sched_post_next(g, pair, 1, nunits);
+            }
+            UnitReader reader;
+            if (!poster) reader.init(g, pair);
+            for (int it = 0; ok; ++it) {
+                unsigned int ticket = 0;
+                if (poster) {
+                    ticket = sched_take(g);                       // for iteration it + 2; looked at after the loads
+                } else {
+                    cur = reader.get(g, pair, npairs, nunits, it, &ok);
+                    if (!ok) { atomicExch(g.err, 25); break; }
+                }
+                const int unit = cur;
+                if (unit < 0) break;
                 const GemmUnit u = decode_unit(g, unit, nkb);
                 const int kb0 = u.kb0, kb1 = u.kb1;
                 const int mb = u.tile / g.tiles_n, nb = u.tile % g.tiles_n;
@@ -540,6 +638,10 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                     }
                     if (++stage == kStages2) { stage = 0; phase ^= 1; }
                 }
+                if (poster) {
+                    cur = ahead1;
+                    ahead1 = sched_post(g, pair, it + 2, ticket, nunits);
+                }
             }
         }
     }
@@ -549,10 +651,14 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            int it = 0;
             const uint32_t a_step = g.a_mn ? 2048u : 32u, b_step = g.b_mn ? 2048u : 32u;
             const uint32_t a_lbo = g.a_mn ? 8192u : 16u, b_lbo = g.b_mn ? 8192u : 16u;
-            for (int unit = pair; unit < nunits && ok; unit += npairs, ++it) {
+            UnitReader reader;
+            reader.init(g, pair);
+            for (int it = 0; ok; ++it) {
+                const int unit = reader.get(g, pair, npairs, nunits, it, &ok);
+                if (!ok) { atomicExch(g.err, 26); break; }
+                if (unit < 0) break;
                 const GemmUnit u = decode_unit(g, unit, nkb);
                 const int kb0 = u.kb0, kb1 = u.kb1;
                 const int acc = it & 1;
@@ -582,8 +688,14 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         const int q = warp & 3;
         const uint32_t tempty_leader = map_to_cta(bar_tempty, 0);
         uint8_t *stg = smem + kStages2 * (kAStage2 + kBStage2) + 256 + q * kStgWarp;
-        int it = 0;
-        for (int unit = pair; unit < nunits; unit += npairs, ++it) {
+        bool ok = true;
+        UnitReader reader;
+        reader.init(g, pair);
+        for (int it = 0; ; ++it) {
+            // every lane reads the mailbox itself (same word: one broadcast access)
+            const int unit = reader.get(g, pair, npairs, nunits, it, &ok);
+            if (!ok) { if (lane == 0) atomicExch(g.err, 27); break; }
+            if (unit < 0) break;
             const GemmUnit u = decode_unit(g, unit, nkb);
             const int sp = u.sp;
             const int mb = u.tile / g.tiles_n, nb = u.tile % g.tiles_n;
@@ -731,6 +843,24 @@ int choose_ksplit(int64_t tiles, int workers, int nkb) {
 }
 
 // ---- host side --------------------------------------------------------------------------
+// Scheduler words of the dynamic tile order: a few sets used in turn, so that products on different streams do not
+// share one; a set is refilled (0xFF) on the product's stream right before its launch.
+constexpr int kSchedSets = 16;
+__device__ unsigned long long g_sched_words[kSchedSets][kSchedWords];
+
+unsigned long long *next_sched_set() {
+    static unsigned long long *base[64] = {nullptr};
+    static std::atomic<unsigned> turn{0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!base[dev]) {
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_sched_words) != cudaSuccess) return nullptr;
+        base[dev] = static_cast<unsigned long long *>(p);
+    }
+    return base[dev] + (size_t)(turn.fetch_add(1) % kSchedSets) * kSchedWords;
+}
+
 PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
     static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
     if (!fn) {
@@ -775,7 +905,7 @@ static int gemm_plan(int64_t m, int64_t n, int64_t k_dim, bool has_bias, bool *t
     SRUB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     const int64_t tiles256 = ((m + 255) / 256) * ((n + BN - 1) / BN);
     // measured: from about 32 tiles of 256 x 256 on, the pair kernel beats twice as many 128 x 256 tiles on single CTAs
-    bool pair = tiles256 >= 32;
+    bool pair = tiles256 >= 32 && m > 160;   // a 256-row tile over at most 160 rows is mostly padding
     if (const char *e = getenv("SRU_B200_GEMM_2SM")) pair = (*e == '1');
     const int64_t tiles = pair ? tiles256 : ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
     const int nkb = (int)((k_dim + BK - 1) / BK);
@@ -881,7 +1011,19 @@ static int gemm_impl(void *c, const void *a, const void *b, const float *col_bia
                                              kSmemBytes2));
         attr_set[dev] = true;
     }
+    g.sched = nullptr;
     if (two_sm) {
+        // Dynamic tile order (SRU_B200_GEMM_DYNAMIC=1) once there is more than one round of units.  It is meant for
+        // products that share the GPU with another kernel (the gradient all-reduce of data-parallel training, whose
+        // host side switches it on); alone on the GPU the static order is as fast or faster.
+        const char *dyn = getenv("SRU_B200_GEMM_DYNAMIC");
+        const int64_t npairs_l = std::min<int64_t>(ntiles, sms / 2);
+        if (dyn && atoi(dyn) != 0 && ntiles > npairs_l && npairs_l <= kSchedMaxPairs) {
+            g.sched = next_sched_set();
+            if (g.sched)
+                SRUB_CUDA_CHECK(cudaMemsetAsync(g.sched, 0xFF, (size_t)(1 + npairs_l * kSchedRing) * sizeof(unsigned long long),
+                                                static_cast<cudaStream_t>(stream)));
+        }
         cudaLaunchConfig_t cfg;
         memset(&cfg, 0, sizeof(cfg));
         cfg.gridDim = dim3(2u * (unsigned)std::min<int64_t>(ntiles, sms / 2), 1, 1);

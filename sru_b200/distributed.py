@@ -11,6 +11,7 @@ of it), and starts that layer's all-reduce asynchronously as soon as autograd ha
 last gradient of the layer, so the collective of layer i overlaps the backward of layers < i.
 Works with any ``torch.distributed`` backend (NCCL on GPUs, gloo in the CPU tests).
 """
+import os
 from typing import Dict, List, Optional
 
 import torch
@@ -39,6 +40,10 @@ class LayerGradAllReducer:
     def __init__(self, model: nn.Module, process_group=None, groups: Optional[List[List[nn.Parameter]]] = None):
         self.group = process_group
         self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        if self.world > 1:
+            # the all-reduces run next to backward and take SMs from it for a while: let the persistent GEMM hand
+            # out its tiles dynamically so that pairs that start late simply take fewer (explicit settings win)
+            os.environ.setdefault("SRU_B200_GEMM_DYNAMIC", "1")
         if groups is None:
             groups = []
             seen = set()

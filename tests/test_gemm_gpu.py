@@ -169,3 +169,31 @@ def test_gemm_tail_split(mn):
     _lib.check_device_error()
     assert rel_err(out32, ref) <= 1e-4 and rel_err(out16, ref) <= 1e-2 and rel_err(acc, ref + base) <= 1e-4
     assert rel_err(out32, plain32) <= 1e-5
+
+
+@pytest.mark.parametrize("layout", ["nn", "nt", "tn"])
+@pytest.mark.parametrize("size", [(4096, 3072, 1024), (256 * 37, 256 * 9, 320), (2048, 6144, 64), (1000, 6144, 2048)])
+def test_gemm_dynamic_tile_order(size, layout):
+    """SRU_B200_GEMM_DYNAMIC=1: the CTA pairs take their tiles from a global counter (posted through a mailbox to
+    both CTAs and all roles) instead of a fixed stride.  Same results, bit for bit: a tile is computed whole by
+    whichever pair takes it.  Shapes with many rounds, with one k-block per tile, and with ragged edges."""
+    import os
+    from sru_b200 import _lib
+    gemm = _gemm()
+    M, N, K = size
+    g = torch.Generator().manual_seed(M + K)
+    ta, tb = layout[0] == "t", layout[1] == "t"
+    a = (torch.randn((K, M) if ta else (M, K), generator=g) * 0.5).bfloat16().to(DEV)
+    b = (torch.randn((N, K) if tb else (K, N), generator=g) * 0.5).bfloat16().to(DEV)
+    static = gemm(a, b, trans_a=ta, trans_b=tb)
+    os.environ["SRU_B200_GEMM_DYNAMIC"] = "1"
+    try:
+        for _ in range(3):       # several launches: the scheduler words are refilled per launch
+            dyn = gemm(a, b, trans_a=ta, trans_b=tb)
+            dyn32 = gemm(a, b, trans_a=ta, trans_b=tb, out_dtype=torch.float32)
+    finally:
+        os.environ.pop("SRU_B200_GEMM_DYNAMIC", None)
+    torch.cuda.synchronize()
+    _lib.check_device_error()
+    assert torch.equal(dyn, static)
+    assert rel_err(dyn32, _ref(a, b, ta, tb)) <= 1e-4
