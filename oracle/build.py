@@ -16,7 +16,9 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_ROOT = os.environ.get("SRU_REFERENCE_ROOT", "/root/reference")
+# the reference checkout: $SRU_REFERENCE_ROOT, or a directory "reference" beside this repository
+REF_ROOT = os.environ.get("SRU_REFERENCE_ROOT",
+                          os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 ORACLE_SO = os.path.join(HERE, "libsru_oracle.so")
 REF_DIR = os.path.join(HERE, "_ref")
 REF_SO = os.path.join(REF_DIR, "libsru_cpu_ref.so")

@@ -2,7 +2,7 @@
 
 Run where the reference checkout is importable (it is not needed at test time):
 
-    SRU_REFERENCE_ROOT=/root/reference python tests/golden/make_golden.py
+    SRU_REFERENCE_ROOT=<reference checkout> python tests/golden/make_golden.py
 
 What is recorded
 * ``op_cases.pt``    -- inputs/outputs/gradients of the reference's
@@ -28,7 +28,8 @@ import warnings
 
 import torch
 
-REF = os.environ.get("SRU_REFERENCE_ROOT", "/root/reference")
+_REPO = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+REF = os.environ.get("SRU_REFERENCE_ROOT", os.path.join(os.path.dirname(_REPO), "reference"))
 os.environ.setdefault("TORCH_EXTENSIONS_DIR", "/tmp/sru_ref_torch_ext")
 sys.path.insert(0, REF)
 warnings.filterwarnings("ignore")
