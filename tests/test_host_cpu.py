@@ -87,6 +87,41 @@ def test_library_exports_every_declared_symbol():
     assert lib.sru_b200_version() >= 100
 
 
+def test_ctypes_signatures_match_the_header():
+    """The Python binding declares, for every entry point it calls, as many arguments as the C prototype has, with
+    pointer / integer / floating kinds in the same positions."""
+    header = open(os.path.join(ROOT, "include", "sru_b200.h")).read()
+    header = re.sub(r"/\*.*?\*/", " ", header, flags=re.S)
+    protos = dict(re.findall(r"\b(sru_b200_[a-z0-9_]+)\s*\(([^)]*)\)\s*;", header))
+    lib = _lib.lib()
+
+    def kind_c(param):
+        param = param.strip()
+        if "*" in param:
+            return "ptr"
+        if param.startswith("double") or param.startswith("float"):
+            return "real"
+        return "int"
+
+    def kind_py(t):
+        if t in (ctypes.c_void_p, ctypes.c_char_p):
+            return "ptr"
+        if t in (ctypes.c_double, ctypes.c_float):
+            return "real"
+        return "int"
+
+    checked = 0
+    for name, params in protos.items():
+        fn = getattr(lib, name)
+        if fn.argtypes is None:
+            continue
+        params = [p for p in params.split(",") if p.strip() and p.strip() != "void"]
+        assert len(params) == len(fn.argtypes), (name, len(params), len(fn.argtypes))
+        assert [kind_c(p) for p in params] == [kind_py(t) for t in fn.argtypes], name
+        checked += 1
+    assert checked >= 8
+
+
 def test_argument_validation_without_gpu():
     L = _lib.lib()
     rc = L.sru_b200_scan_forward(None, None, None, None, None, None, None, None, None, None,
