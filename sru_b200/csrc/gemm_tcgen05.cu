@@ -440,9 +440,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 constexpr int kStages2 = 5;
 constexpr int kAStage2 = 128 * BK * 2;   // 16 KB: this CTA's 128 rows of A
 constexpr int kBStage2 = 128 * BK * 2;   // 16 KB: this CTA's 128 columns of B
-constexpr int kStgRow = 128 * 2 + 16;          // staged output row: 128 16-bit columns + 16 B pad (bank spread)
+// Eight epilogue warps per CTA: TMEM lanes 32q..32q+31 (rows) can only be read by warps with warp % 4 == q, so the two
+// warps of a quarter share its 32 rows and take one 128-column half of the tile each.  With short reductions
+// (K = 512: 8 k-blocks per tile) the epilogue of a tile, not its MMAs, sets the pace; eight warps halve it.
+constexpr int kEpiWarps2 = 8;
+constexpr int kThreads2 = 64 + 32 * kEpiWarps2;
+constexpr int kStgRow = 128 * 2;               // staged output row: 128 16-bit columns, 16-byte chunks XOR-swizzled by row
 constexpr int kStgWarp = 32 * kStgRow;         // per epilogue warp
-constexpr int kSmemBytes2 = kStages2 * (kAStage2 + kBStage2) + 1024 + 256 + 4 * kStgWarp;
+constexpr int kSmemBytes2 = kStages2 * (kAStage2 + kBStage2) + 1024 + 256 + kEpiWarps2 * kStgWarp;
+static_assert(kSmemBytes2 <= 227 * 1024, "pair kernel shared memory");
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -500,12 +506,11 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t adesc, uin
 // one output row: every store instruction then writes two full 256-byte row segments.
 template <typename TO>
 __device__ __forceinline__ void epilogue_staged(const GemmArgs &g, uint32_t tmem_warp, int64_t row0, int64_t col_base,
-                                                uint8_t *stg, int lane) {
+                                                uint8_t *stg, int lane, int h) {
     const int64_t row = row0 + lane;
-#pragma unroll 1
-    for (int h = 0; h < 2; ++h) {
+    {
         const int64_t colh = col_base + h * 128;
-        if (colh >= g.N) break;
+        if (colh >= g.N) return;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
             const int64_t col0 = colh + c * 32;
@@ -531,7 +536,9 @@ __device__ __forceinline__ void epilogue_staged(const GemmArgs &g, uint32_t tmem
                         for (int j = 0; j < 8; ++j) v[j] += Cvt<TO>::to_f(crow[j]);
                     }
                 }
-                store8<TO>(reinterpret_cast<TO *>(stg + lane * kStgRow + (c * 32 + j0) * 2), v);
+                // 16-byte chunk (c*4 + j0/8) of this lane's row, XOR-swizzled so that the eight lanes of a
+                // shared-memory phase hit eight different bank groups
+                store8<TO>(reinterpret_cast<TO *>(stg + lane * kStgRow + (((c * 4 + (j0 >> 3)) ^ (lane & 15)) << 4)), v);
             }
         }
         __syncwarp();
@@ -541,7 +548,7 @@ __device__ __forceinline__ void epilogue_staged(const GemmArgs &g, uint32_t tmem
         for (int rr = 0; rr < 32; rr += 2) {
             const int rl = rr + sub;
             if (row0 + rl < g.M && col < g.N) {
-                const uint4 val = *reinterpret_cast<const uint4 *>(stg + rl * kStgRow + seg * 16);
+                const uint4 val = *reinterpret_cast<const uint4 *>(stg + rl * kStgRow + ((seg ^ (rl & 15)) << 4));
                 *reinterpret_cast<uint4 *>(reinterpret_cast<TO *>(g.c) + (row0 + rl) * g.ldc + col) = val;
             }
         }
@@ -549,7 +556,7 @@ __device__ __forceinline__ void epilogue_staged(const GemmArgs &g, uint32_t tmem
     }
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads2, 1)
 gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                         const GemmArgs g) {
     extern __shared__ uint8_t smem_raw[];
@@ -573,7 +580,7 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages2; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(bar_tfull + 8 * i, 1); mbar_init(bar_tempty + 8 * i, 8); }
+        for (int i = 0; i < 2; ++i) { mbar_init(bar_tfull + 8 * i, 1); mbar_init(bar_tempty + 8 * i, 2 * kEpiWarps2); }
         fence_mbar_init();
     }
     if (warp == 1) {
@@ -685,9 +692,10 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         }
     } else {
         // ------------------------------ epilogue (both CTAs, own rows) ------------------------------
-        const int q = warp & 3;
+        const int q = warp & 3;                 // TMEM lane quarter = 32 rows of the CTA's 128
+        const int hsel = (warp - 2) >> 2;       // which 128-column half of the tile this warp converts
         const uint32_t tempty_leader = map_to_cta(bar_tempty, 0);
-        uint8_t *stg = smem + kStages2 * (kAStage2 + kBStage2) + 256 + q * kStgWarp;
+        uint8_t *stg = smem + kStages2 * (kAStage2 + kBStage2) + 256 + (warp - 2) * kStgWarp;
         bool ok = true;
         UnitReader reader;
         reader.init(g, pair);
@@ -714,19 +722,19 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 gp.ldc = 256; gp.N = 256; gp.bias = nullptr; gp.accumulate = 0;
                 const int64_t lrow = (int64_t)rank * 128 + q * 32 + lane;
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
+                for (int c = hsel * 4; c < hsel * 4 + 4; ++c) {
                     uint32_t r[32];
                     tmem_ld32(tmem_warp + c * 32, r);
                     tmem_ld_wait();
                     epilogue_chunk<float>(gp, r, lrow, c * 32);
                 }
             } else if (g.c_dtype == SRU_BF16) {
-                epilogue_staged<__nv_bfloat16>(g, tmem_warp, row0, col_base, stg, lane);
+                epilogue_staged<__nv_bfloat16>(g, tmem_warp, row0, col_base, stg, lane, hsel);
             } else if (g.c_dtype == SRU_F16) {
-                epilogue_staged<__half>(g, tmem_warp, row0, col_base, stg, lane);
+                epilogue_staged<__half>(g, tmem_warp, row0, col_base, stg, lane, hsel);
             } else {
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
+                for (int c = hsel * 4; c < hsel * 4 + 4; ++c) {
                     const int64_t col0 = col_base + c * 32;
                     if (col0 >= g.N) break;
                     uint32_t r[32];
@@ -1027,7 +1035,7 @@ static int gemm_impl(void *c, const void *a, const void *b, const float *col_bia
         cudaLaunchConfig_t cfg;
         memset(&cfg, 0, sizeof(cfg));
         cfg.gridDim = dim3(2u * (unsigned)std::min<int64_t>(ntiles, sms / 2), 1, 1);
-        cfg.blockDim = dim3(kThreads, 1, 1);
+        cfg.blockDim = dim3(kThreads2, 1, 1);
         cfg.dynamicSmemBytes = kSmemBytes2;
         cfg.stream = static_cast<cudaStream_t>(stream);
         cudaLaunchAttribute attr[1];

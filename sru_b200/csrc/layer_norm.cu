@@ -186,16 +186,36 @@ ln_fwd_kernel(TO *__restrict__ y, float *__restrict__ mean_out, float *__restric
 
     const int64_t stride = (int64_t)gridDim.x * RPC;
     int64_t base = (int64_t)blockIdx.x * RPC;
-    Raw A, B;
-    if (base < rows) load(A, base);
-    while (base < rows) {
+    if constexpr (sizeof(TI) == 2) {
+        // 16-bit rows are half the bytes: two rows ahead (three buffers in turn) to keep as much in flight
+        Raw A, B, C;
+        if (base < rows) load(A, base);
         if (base + stride < rows) load(B, base + stride);
-        process(A, base);
-        base += stride;
-        if (base >= rows) break;
-        if (base + stride < rows) load(A, base + stride);
-        process(B, base);
-        base += stride;
+        while (base < rows) {
+            if (base + 2 * stride < rows) load(C, base + 2 * stride);
+            process(A, base);
+            base += stride;
+            if (base >= rows) break;
+            if (base + 2 * stride < rows) load(A, base + 2 * stride);
+            process(B, base);
+            base += stride;
+            if (base >= rows) break;
+            if (base + 2 * stride < rows) load(B, base + 2 * stride);
+            process(C, base);
+            base += stride;
+        }
+    } else {
+        Raw A, B;
+        if (base < rows) load(A, base);
+        while (base < rows) {
+            if (base + stride < rows) load(B, base + stride);
+            process(A, base);
+            base += stride;
+            if (base >= rows) break;
+            if (base + stride < rows) load(A, base + stride);
+            process(B, base);
+            base += stride;
+        }
     }
 }
 
