@@ -69,6 +69,7 @@ struct GemmArgs {
     // Dynamic tile order (pair kernel): word 0 is the next-unit counter, then kSchedRing mailbox words per CTA pair.
     // NULL: static order (unit = pair, pair + pairs, ...).
     unsigned long long *sched;
+    int epi_warps;      // pair kernel instance: 8 or 4 epilogue warps per CTA (host side only)
     int *err;
 };
 
@@ -556,7 +557,8 @@ __device__ __forceinline__ void epilogue_staged(const GemmArgs &g, uint32_t tmem
     }
 }
 
-__global__ void __launch_bounds__(kThreads2, 1)
+template <int EW>     // working epilogue warps per CTA: 4 (192 threads) or 8 (320 threads)
+__global__ void __launch_bounds__(64 + 32 * EW, 1)
 gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                         const GemmArgs g) {
     extern __shared__ uint8_t smem_raw[];
@@ -580,7 +582,7 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages2; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(bar_tfull + 8 * i, 1); mbar_init(bar_tempty + 8 * i, 2 * kEpiWarps2); }
+        for (int i = 0; i < 2; ++i) { mbar_init(bar_tfull + 8 * i, 1); mbar_init(bar_tempty + 8 * i, 2 * EW); }
         fence_mbar_init();
     }
     if (warp == 1) {
@@ -692,8 +694,12 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         }
     } else {
         // ------------------------------ epilogue (both CTAs, own rows) ------------------------------
+        // Eight warps (EW = 8) when the reduction is short and the epilogue sets the pace; with long reductions four,
+        // each doing both column halves: eight put two busy warps on the scheduler of the MMA-issuing thread and the
+        // tensor pipe loses 7 % (ncu: 92 % -> 85 % active on the K = 2048 forward product).
         const int q = warp & 3;                 // TMEM lane quarter = 32 rows of the CTA's 128
-        const int hsel = (warp - 2) >> 2;       // which 128-column half of the tile this warp converts
+        const int h_first = (EW == 8) ? ((warp - 2) >> 2) : 0;   // 128-column halves this warp converts
+        const int h_last = (EW == 8) ? h_first : 1;
         const uint32_t tempty_leader = map_to_cta(bar_tempty, 0);
         uint8_t *stg = smem + kStages2 * (kAStage2 + kBStage2) + 256 + (warp - 2) * kStgWarp;
         bool ok = true;
@@ -722,19 +728,21 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 gp.ldc = 256; gp.N = 256; gp.bias = nullptr; gp.accumulate = 0;
                 const int64_t lrow = (int64_t)rank * 128 + q * 32 + lane;
 #pragma unroll 1
-                for (int c = hsel * 4; c < hsel * 4 + 4; ++c) {
+                for (int c = h_first * 4; c < h_last * 4 + 4; ++c) {
                     uint32_t r[32];
                     tmem_ld32(tmem_warp + c * 32, r);
                     tmem_ld_wait();
                     epilogue_chunk<float>(gp, r, lrow, c * 32);
                 }
             } else if (g.c_dtype == SRU_BF16) {
-                epilogue_staged<__nv_bfloat16>(g, tmem_warp, row0, col_base, stg, lane, hsel);
+                for (int h = h_first; h <= h_last; ++h)
+                    epilogue_staged<__nv_bfloat16>(g, tmem_warp, row0, col_base, stg, lane, h);
             } else if (g.c_dtype == SRU_F16) {
-                epilogue_staged<__half>(g, tmem_warp, row0, col_base, stg, lane, hsel);
+                for (int h = h_first; h <= h_last; ++h)
+                    epilogue_staged<__half>(g, tmem_warp, row0, col_base, stg, lane, h);
             } else {
 #pragma unroll 1
-                for (int c = hsel * 4; c < hsel * 4 + 4; ++c) {
+                for (int c = h_first * 4; c < h_last * 4 + 4; ++c) {
                     const int64_t col0 = col_base + c * 32;
                     if (col0 >= g.N) break;
                     uint32_t r[32];
@@ -1015,11 +1023,15 @@ static int gemm_impl(void *c, const void *a, const void *b, const float *col_bia
     if (dev < 64 && !attr_set[dev]) {
         SRUB_CUDA_CHECK(cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              kSmemBytes));
-        SRUB_CUDA_CHECK(cudaFuncSetAttribute(gemm_tcgen05_2sm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        SRUB_CUDA_CHECK(cudaFuncSetAttribute(gemm_tcgen05_2sm_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             kSmemBytes2));
+        SRUB_CUDA_CHECK(cudaFuncSetAttribute(gemm_tcgen05_2sm_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              kSmemBytes2));
         attr_set[dev] = true;
     }
     g.sched = nullptr;
+    g.epi_warps = (nkb_all <= 16) ? 8 : 4;      // see the epilogue of the pair kernel
+    if (const char *e = getenv("SRU_B200_GEMM_EPI_WARPS")) g.epi_warps = (atoi(e) == 8) ? 8 : 4;
     if (two_sm) {
         // Dynamic tile order (SRU_B200_GEMM_DYNAMIC=1) once there is more than one round of units.  It is meant for
         // products that share the GPU with another kernel (the gradient all-reduce of data-parallel training, whose
@@ -1035,7 +1047,7 @@ static int gemm_impl(void *c, const void *a, const void *b, const float *col_bia
         cudaLaunchConfig_t cfg;
         memset(&cfg, 0, sizeof(cfg));
         cfg.gridDim = dim3(2u * (unsigned)std::min<int64_t>(ntiles, sms / 2), 1, 1);
-        cfg.blockDim = dim3(kThreads2, 1, 1);
+        cfg.blockDim = dim3(64 + 32 * g.epi_warps, 1, 1);
         cfg.dynamicSmemBytes = kSmemBytes2;
         cfg.stream = static_cast<cudaStream_t>(stream);
         cudaLaunchAttribute attr[1];
@@ -1043,7 +1055,8 @@ static int gemm_impl(void *c, const void *a, const void *b, const float *col_bia
         attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        SRUB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tcgen05_2sm_kernel, map_a, map_b, g));
+        if (g.epi_warps == 8) SRUB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tcgen05_2sm_kernel<8>, map_a, map_b, g));
+        else SRUB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tcgen05_2sm_kernel<4>, map_a, map_b, g));
     } else {
         const unsigned grid = (unsigned)std::min<int64_t>(ntiles, sms);
         gemm_tcgen05_kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(map_a, map_b, g);
