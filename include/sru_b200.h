@@ -62,6 +62,34 @@ const char *sru_b200_last_error(void);
 int sru_b200_check_device_error(void *stream);
 
 /*
+ * Tuning and diagnostic options.  No counterpart in the reference (its launch configuration is fixed,
+ * sru/csrc/sru_cuda_kernel.cu:841-846).  Every option starts "not set" (the library chooses) or from
+ * the environment variable SRU_B200_<NAME IN CAPITALS>, which is read once per process; afterwards only
+ * these calls change it.  A negative value un-sets an option.  Process-wide, not per stream.
+ *   fwd_v, bwd_v                       columns per thread of the pipelined scans (1, 2, 4)
+ *   scan_threads, fwd_threads, bwd_threads   consumer threads per CTA (32..128)
+ *   scan_ss, scan_stages               time steps per ring stage, ring depth
+ *   force_generic                      1: always the one-thread-per-column kernels
+ *   fwd_split                          forward scan with the state chain and the output arithmetic on
+ *                                      separate warps: 1 always (where the shape allows), 0 never
+ *   gemm_ksplit, gemm_2sm, gemm_epi_warps    K slabs, pair kernel on/off, epilogue warps (4 or 8)
+ *   gemm_dynamic                       1: the pair GEMM hands out its tiles dynamically (needs the
+ *                                      workspace form of the call); for products that share the GPU with
+ *                                      a collective
+ * Unknown names give SRU_ERR_BAD_ARG.  sru_b200_get_option returns the value, or -1 when not set.
+ */
+int sru_b200_set_option(const char *name, int value);
+int sru_b200_get_option(const char *name);
+
+/*
+ * Which kernel family served the calling thread's most recent scan call (forward or backward):
+ * 0 none yet / the call failed before a launch, 1 pipelined (TMA ring, registers across time),
+ * 2 generic (one thread per column: custom V, tanh, odd hidden sizes, unaligned pointers, fp64),
+ * 3 pipelined with split roles (forward, few columns).  No counterpart in the reference.
+ */
+int sru_b200_last_scan_kernel(void);
+
+/*
  * Forward scan.  Replaces the four forward launchers of the reference,
  * sru_cuda_forward_simple / sru_cuda_bi_forward_simple / sru_cuda_forward /
  * sru_cuda_bi_forward (sru/csrc/sru_cuda_kernel.cu:827-860, :911-944, :995-1036,
@@ -184,9 +212,10 @@ int sru_b200_gemm(
  * The same contraction with caller-provided scratch.  Products whose output tiles alone
  * cannot fill the GPU but whose reduction is long (the weight gradient x^T grad_U:
  * M = input width, K = length * batch) are cut into K slabs whose fp32 partial results go to
- * `workspace` and are summed by a second small kernel.  sru_b200_gemm_workspace_bytes()
- * says how much scratch such a split wants (0: no split); with a NULL or smaller workspace
- * the call behaves exactly like sru_b200_gemm.  Same library-GEMM counterpart in the
+ * `workspace` and are summed by a second small kernel.  With the option gemm_dynamic the pair
+ * kernel also keeps its tile counter and mailboxes there.  sru_b200_gemm_workspace_bytes()
+ * says how much scratch the call wants (0: none); with a NULL or smaller workspace
+ * the call behaves exactly like sru_b200_gemm.  Calls that share one workspace must be stream-ordered.  Same library-GEMM counterpart in the
  * reference as sru_b200_gemm (sru/modules.py:363-378 and its autograd).
  */
 size_t sru_b200_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k_dim, int has_bias);

@@ -14,7 +14,7 @@
  * re-exported by tests/golden/make_golden.py.
  *
  * Reference lines each function follows are cited in sru_oracle_body.inc.
- * Build: see oracle/Makefile (gcc -O2 -fopenmp -shared -fPIC).
+ * Build: oracle/build.py (gcc -O2 -fno-fast-math -ffp-contract=off -fopenmp -shared -fPIC).
  */
 #include <math.h>
 #include <stdlib.h>

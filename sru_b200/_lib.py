@@ -40,6 +40,12 @@ def lib():
         l.sru_b200_last_error.restype = ctypes.c_char_p
         l.sru_b200_check_device_error.restype = _int
         l.sru_b200_check_device_error.argtypes = [_vp]
+        l.sru_b200_set_option.restype = _int
+        l.sru_b200_set_option.argtypes = [ctypes.c_char_p, _int]
+        l.sru_b200_get_option.restype = _int
+        l.sru_b200_get_option.argtypes = [ctypes.c_char_p]
+        l.sru_b200_last_scan_kernel.restype = _int
+        l.sru_b200_last_scan_kernel.argtypes = []
         l.sru_b200_scan_forward.restype = _int
         l.sru_b200_scan_forward.argtypes = [_vp] * 10 + [_i64, _i64, _i64, _int, _int, _int, _int, _int,
                                                          ctypes.c_double, _int, _int, _vp]
@@ -74,6 +80,40 @@ def load_torch_ops():
         lib()
         torch.ops.load_library(TORCH_LIB_PATH)
         _torch_ops_loaded = True
+
+
+SCAN_KERNEL_NAMES = {0: "none", 1: "pipelined", 2: "generic", 3: "split"}
+
+
+def set_option(name: str, value: int) -> None:
+    """Sets a tuning option of the native library (see include/sru_b200.h); negative un-sets it."""
+    check(lib().sru_b200_set_option(name.encode(), int(value)))
+
+
+def get_option(name: str) -> int:
+    return int(lib().sru_b200_get_option(name.encode()))
+
+
+class options:
+    """Context manager: ``with options(fwd_v=2, scan_stages=3): ...`` sets, then restores."""
+
+    def __init__(self, **kw):
+        self.kw = {k: v for k, v in kw.items() if v is not None}
+
+    def __enter__(self):
+        self.old = {k: get_option(k) for k in self.kw}
+        for k, v in self.kw.items():
+            set_option(k, v)
+        return self
+
+    def __exit__(self, *exc):
+        for k, v in self.old.items():
+            set_option(k, v)
+
+
+def last_scan_kernel() -> str:
+    """'pipelined', 'generic', 'split' or 'none': what this thread's last scan call launched."""
+    return SCAN_KERNEL_NAMES.get(int(lib().sru_b200_last_scan_kernel()), "unknown")
 
 
 def check(rc):

@@ -1,8 +1,12 @@
 // extern "C" entry points of libsru_b200.so (declared in include/sru_b200.h): argument
 // validation, dispatch between the pipelined and the generic scan kernels, error plumbing.
+#include <atomic>
+#include <cctype>
 #include <cstdarg>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
+#include <string>
 
 #include "scan.cuh"
 
@@ -17,6 +21,38 @@ int set_error(int code, const char *fmt, ...) {
     va_end(ap);
     return code;
 }
+
+// ---- options: environment defaults read once, then changed only through sru_b200_set_option ----
+static const char *const kOptionNames[OPT_COUNT] = {
+    "fwd_v", "bwd_v", "scan_threads", "fwd_threads", "bwd_threads", "scan_ss", "scan_stages",
+    "force_generic", "fwd_split", "gemm_ksplit", "gemm_2sm", "gemm_epi_warps", "gemm_dynamic"};
+static std::atomic<int> g_options[OPT_COUNT];
+static std::once_flag g_options_once;
+
+static void load_option_defaults() {
+    for (int i = 0; i < OPT_COUNT; ++i) {
+        std::string env = "SRU_B200_";
+        for (const char *c = kOptionNames[i]; *c; ++c) env.push_back((char)toupper((unsigned char)*c));
+        const char *e = getenv(env.c_str());
+        g_options[i].store((e && *e) ? atoi(e) : -1);
+    }
+}
+
+int option(Option o, int dflt) {
+    std::call_once(g_options_once, load_option_defaults);
+    const int v = g_options[o].load(std::memory_order_relaxed);
+    return v < 0 ? dflt : v;
+}
+
+static int find_option(const char *name) {
+    if (!name) return -1;
+    for (int i = 0; i < OPT_COUNT; ++i)
+        if (strcmp(name, kOptionNames[i]) == 0) return i;
+    return -1;
+}
+
+static thread_local int tl_scan_kernel = SCAN_KERNEL_NONE;
+void note_scan_kernel(int which) { tl_scan_kernel = which; }
 
 __device__ int g_device_error = 0;
 
@@ -76,7 +112,23 @@ using namespace srub;
 
 extern "C" {
 
-int sru_b200_version(void) { return 100; }
+int sru_b200_version(void) { return 200; }
+
+int sru_b200_set_option(const char *name, int value) {
+    const int i = find_option(name);
+    if (i < 0) return set_error(SRU_ERR_BAD_ARG, "unknown option '%s'", name ? name : "(null)");
+    std::call_once(g_options_once, load_option_defaults);
+    g_options[i].store(value < 0 ? -1 : value);
+    return 0;
+}
+
+int sru_b200_get_option(const char *name) {
+    const int i = find_option(name);
+    if (i < 0) return set_error(SRU_ERR_BAD_ARG, "unknown option '%s'", name ? name : "(null)");
+    return option(static_cast<Option>(i), -1);
+}
+
+int sru_b200_last_scan_kernel(void) { return tl_scan_kernel; }
 
 const char *sru_b200_last_error(void) { return tl_error; }
 
@@ -114,8 +166,10 @@ int sru_b200_scan_forward(void *h, void *c_hist, void *c_last, const void *u, co
     a.activation_type = activation_type; a.skip_type = skip_type; a.is_custom = is_custom ? 1 : 0;
     a.scale_x = scale_x; a.dtype = dtype; a.c_dtype = c_dtype;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    rc = launch_scan_pipelined(a, false, st);
+    note_scan_kernel(SCAN_KERNEL_NONE);
+    rc = launch_scan_pipelined(a, false, st);   // notes which of its kernel families took the call
     if (rc != 0) return rc < 0 ? rc : 0;
+    note_scan_kernel(SCAN_KERNEL_GENERIC);
     return launch_scan_generic(a, false, st);
 }
 
@@ -153,8 +207,10 @@ int sru_b200_scan_backward(void *grad_u, void *grad_x, void *grad_wc, void *grad
     a.activation_type = activation_type; a.skip_type = skip_type; a.is_custom = is_custom ? 1 : 0;
     a.scale_x = scale_x; a.dtype = dtype; a.c_dtype = c_dtype;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    note_scan_kernel(SCAN_KERNEL_NONE);
     rc = launch_scan_pipelined(a, true, st);
     if (rc != 0) return rc < 0 ? rc : 0;
+    note_scan_kernel(SCAN_KERNEL_GENERIC);
     return launch_scan_generic(a, true, st);
 }
 

@@ -19,6 +19,20 @@ int set_error(int code, const char *fmt, ...);
 int *device_error_flag();  // device int, set non-zero by a kernel whose bounded wait gave up
 int ensure_context();      // binds the device's primary context to this thread if it has none; 0 or SRU_ERR_CUDA
 
+// Tuning / diagnostic options (sru_b200_set_option).  Each starts from the environment variable
+// SRU_B200_<NAME IN CAPITALS>, read ONCE per process on first use; a negative value means "not set,
+// let the library choose".
+enum Option {
+    OPT_FWD_V, OPT_BWD_V, OPT_SCAN_THREADS, OPT_FWD_THREADS, OPT_BWD_THREADS, OPT_SCAN_SS, OPT_SCAN_STAGES,
+    OPT_FORCE_GENERIC, OPT_FWD_SPLIT, OPT_GEMM_KSPLIT, OPT_GEMM_2SM, OPT_GEMM_EPI_WARPS, OPT_GEMM_DYNAMIC,
+    OPT_COUNT
+};
+int option(Option o, int dflt);   // the option's value, or dflt when it is not set
+
+// Which scan kernel family the calling thread's most recent scan launch used (sru_b200_last_scan_kernel).
+enum { SCAN_KERNEL_NONE = 0, SCAN_KERNEL_PIPELINED = 1, SCAN_KERNEL_GENERIC = 2, SCAN_KERNEL_SPLIT = 3 };
+void note_scan_kernel(int which);
+
 #define SRUB_CUDA_CHECK(expr)                                                              \
     do {                                                                                   \
         cudaError_t err__ = (expr);                                                        \

@@ -34,7 +34,6 @@
 #include <cudaTypedefs.h>
 
 #include <algorithm>
-#include <atomic>
 #include <cstdlib>
 #include <cstring>
 
@@ -61,11 +60,6 @@ struct GemmArgs {
     uint32_t idesc;
     int tiles_m, tiles_n;
     int ksplit, kbps;   // split-K: partial products over kbps k-blocks each go to slab sp of an fp32 workspace
-    // Tail split (pair kernel): tiles [0, tail_t0) are whole rounds of the persistent grid and are computed in one
-    // piece; each of the remaining tiles is cut into tail_s K slabs of tail_kbps k-blocks whose fp32 256 x 256
-    // partials go to tail_ws[(tile - tail_t0) * tail_s + slab]; tail_reduce finishes them.  tail_s == 0: off.
-    int tail_t0, tail_s, tail_kbps;
-    float *tail_ws;
     // Dynamic tile order (pair kernel): word 0 is the next-unit counter, then kSchedRing mailbox words per CTA pair.
     // NULL: static order (unit = pair, pair + pairs, ...).
     unsigned long long *sched;
@@ -150,30 +144,14 @@ struct UnitReader {
 // One work unit of the persistent loop: a tile (or a K slab of one) and where its result goes.
 struct GemmUnit {
     int tile, kb0, kb1;
-    int sp;      // slab index of a uniform split (result row offset sp * M in the workspace)
-    int slot;    // >= 0: tail split, partial tile number `slot` of tail_ws; -1 otherwise
+    int sp;      // slab index of a split reduction (result row offset sp * M in the workspace)
 };
 __device__ __forceinline__ GemmUnit decode_unit(const GemmArgs &g, int unit, int nkb) {
     GemmUnit u;
-    if (g.tail_s > 0) {
-        u.sp = 0;
-        if (unit < g.tail_t0) {
-            u.tile = unit; u.kb0 = 0; u.kb1 = nkb; u.slot = -1;
-        } else {
-            const int v = unit - g.tail_t0;
-            const int tt = v / g.tail_s, slab = v - tt * g.tail_s;
-            u.tile = g.tail_t0 + tt;
-            u.kb0 = slab * g.tail_kbps;
-            u.kb1 = min(nkb, u.kb0 + g.tail_kbps);
-            u.slot = v;
-        }
-    } else {
-        u.tile = unit / g.ksplit;
-        u.sp = unit - u.tile * g.ksplit;
-        u.kb0 = u.sp * g.kbps;
-        u.kb1 = min(nkb, u.kb0 + g.kbps);
-        u.slot = -1;
-    }
+    u.tile = unit / g.ksplit;
+    u.sp = unit - u.tile * g.ksplit;
+    u.kb0 = u.sp * g.kbps;
+    u.kb1 = min(nkb, u.kb0 + g.kbps);
     return u;
 }
 
@@ -577,7 +555,7 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
     const int ntiles_all = g.tiles_m * g.tiles_n;
     // work units: (256 x 256 tile, K slab)
-    const int nunits = g.tail_s > 0 ? g.tail_t0 + (ntiles_all - g.tail_t0) * g.tail_s : ntiles_all * g.ksplit;
+    const int nunits = ntiles_all * g.ksplit;
     const int nkb = (int)((g.K + BK - 1) / BK);
 
     if (threadIdx.x == 0) {
@@ -721,20 +699,7 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             const int64_t row = row0 + lane;
             const int64_t col_base = (int64_t)nb * BN;
             const uint32_t tmem_warp = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
-            if (u.slot >= 0) {
-                // a K slab of a tail tile: the raw fp32 accumulators, tile-local [256][256]
-                GemmArgs gp = g;
-                gp.c = g.tail_ws + (size_t)u.slot * 65536;
-                gp.ldc = 256; gp.N = 256; gp.bias = nullptr; gp.accumulate = 0;
-                const int64_t lrow = (int64_t)rank * 128 + q * 32 + lane;
-#pragma unroll 1
-                for (int c = h_first * 4; c < h_last * 4 + 4; ++c) {
-                    uint32_t r[32];
-                    tmem_ld32(tmem_warp + c * 32, r);
-                    tmem_ld_wait();
-                    epilogue_chunk<float>(gp, r, lrow, c * 32);
-                }
-            } else if (g.c_dtype == SRU_BF16) {
+            if (g.c_dtype == SRU_BF16) {
                 for (int h = h_first; h <= h_last; ++h)
                     epilogue_staged<__nv_bfloat16>(g, tmem_warp, row0, col_base, stg, lane, h);
             } else if (g.c_dtype == SRU_F16) {
@@ -789,61 +754,11 @@ __global__ void splitk_reduce(const float *__restrict__ ws, int nsplit, int64_t 
     }
 }
 
-// Tail-split finish: tile t0 + tt of C = sum over its K slabs of the fp32 partial tiles (+ C when accumulating).
-template <typename TO>
-__global__ void tail_reduce(const float *__restrict__ ws, int nslab, int t0, int tiles_n, int64_t M, int64_t N,
-                            TO *__restrict__ c, int64_t ldc, int accumulate) {
-    const int tt = blockIdx.x >> 6;                                  // 64 blocks of 256 threads x 4 columns per tile
-    const int e = ((blockIdx.x & 63) * 256 + threadIdx.x) * 4;      // element of the 256 x 256 tile
-    const int r = e >> 8, col = e & 255;
-    const int tile = t0 + tt;
-    const int64_t row = (int64_t)(tile / tiles_n) * 256 + r, gcol = (int64_t)(tile % tiles_n) * 256 + col;
-    if (row >= M || gcol >= N) return;                               // N is a multiple of 8
-    const float *p = ws + (size_t)tt * nslab * 65536 + e;
-    float4 acc = *reinterpret_cast<const float4 *>(p);
-    for (int sp = 1; sp < nslab; ++sp) {
-        const float4 v = *reinterpret_cast<const float4 *>(p + (size_t)sp * 65536);
-        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-    }
-    TO *o = c + row * ldc + gcol;
-    if (accumulate) {
-        acc.x += Cvt<TO>::to_f(o[0]); acc.y += Cvt<TO>::to_f(o[1]);
-        acc.z += Cvt<TO>::to_f(o[2]); acc.w += Cvt<TO>::to_f(o[3]);
-    }
-    o[0] = Cvt<TO>::from_f(acc.x); o[1] = Cvt<TO>::from_f(acc.y);
-    o[2] = Cvt<TO>::from_f(acc.z); o[3] = Cvt<TO>::from_f(acc.w);
-}
-
-// Tail split of a product on the pair kernel.  The persistent grid of `workers` CTA pairs walks the tiles in
-// rounds; with R whole rounds and r tiles left, the last round keeps only r of the workers busy.  Cutting each of
-// the r tiles into S slabs makes ceil(r*S/workers) short rounds of 1/S length instead.  Worth it only when the
-// product has few rounds (a weight gradient: 192 tiles on 74 pairs is 2.6 rounds of work done in 3).
-// OFF unless SRU_B200_GEMM_TAIL=1: measured on B200 it does not pay.  These products run at the board's power
-// limit, where time follows energy; while only 44 of 74 pairs work in the last round the clocks rise, and the
-// product takes the same 4.8 ms with and without the split (and the whole training step the same 215 ms).
-// Returns S (0: no tail split) and the number of whole-round tiles in *t0.
-int choose_tail_split(int64_t tiles, int workers, int nkb, int *t0) {
-    *t0 = 0;
-    const char *e = getenv("SRU_B200_GEMM_TAIL");
-    if (!e || atoi(e) == 0) return 0;
-    const int64_t rounds = tiles / workers, r = tiles % workers;
-    if (rounds < 1 || rounds > 6 || r == 0 || nkb < 128) return 0;
-    int best = 0;
-    double best_len = 1.0;     // length of the last round without a split
-    for (int sp = 2; sp <= 8; ++sp) {
-        if (nkb / sp < 32) break;
-        const double len = (double)((r * sp + workers - 1) / workers) / sp;
-        if (len < best_len - 0.04) { best_len = len; best = sp; }
-    }
-    if (best == 0 || best_len > 0.85) return 0;
-    *t0 = (int)(rounds * workers);
-    return best;
-}
-
 // How many K slabs to cut a product into: only when the tiles alone leave the last wave of the
 // persistent grid badly filled and the reduction is long enough to amortise the extra pass.
 int choose_ksplit(int64_t tiles, int workers, int nkb) {
-    if (getenv("SRU_B200_GEMM_KSPLIT")) return std::max(1, std::min(atoi(getenv("SRU_B200_GEMM_KSPLIT")), 16));
+    const int forced = option(OPT_GEMM_KSPLIT, 0);
+    if (forced > 0) return std::min(forced, 16);
     // Measured on B200: once the tiles fill at least half of the GPU, splitting only costs L2 reuse
     // between concurrently running tiles; it pays (up to 3x) when the grid would be mostly idle.
     if (nkb < 64 || 2 * tiles > (int64_t)workers) return 1;
@@ -859,24 +774,6 @@ int choose_ksplit(int64_t tiles, int workers, int nkb) {
 }
 
 // ---- host side --------------------------------------------------------------------------
-// Scheduler words of the dynamic tile order: a few sets used in turn, so that products on different streams do not
-// share one; a set is refilled (0xFF) on the product's stream right before its launch.
-constexpr int kSchedSets = 16;
-__device__ unsigned long long g_sched_words[kSchedSets][kSchedWords];
-
-unsigned long long *next_sched_set() {
-    static unsigned long long *base[64] = {nullptr};
-    static std::atomic<unsigned> turn{0};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    if (!base[dev]) {
-        void *p = nullptr;
-        if (cudaGetSymbolAddress(&p, g_sched_words) != cudaSuccess) return nullptr;
-        base[dev] = static_cast<unsigned long long *>(p);
-    }
-    return base[dev] + (size_t)(turn.fetch_add(1) % kSchedSets) * kSchedWords;
-}
-
 PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
     static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
     if (!fn) {
@@ -913,30 +810,46 @@ int make_map(CUtensorMap *map, const void *base, int dtype, int64_t inner, int64
 
 using namespace srub;
 
-// Kernel choice for a problem: pair kernel or single-CTA kernel, and the number of K slabs.
-static int gemm_plan(int64_t m, int64_t n, int64_t k_dim, bool has_bias, bool *two_sm, int *ksplit,
-                     int *tail_s, int *tail_t0) {
+// Kernel choice for a problem: pair kernel or single-CTA kernel, the number of K slabs, and whether the pair kernel
+// takes its tiles dynamically (option gemm_dynamic, more than one round of units).
+struct GemmPlan {
+    bool two_sm;
+    int ksplit;        // K slabs (1: none); needs ksplit * m * n floats of workspace
+    bool dynamic;      // dynamic tile order; needs sched_bytes of workspace
+    int64_t units;     // work units of the persistent loop (tiles x slabs)
+    int workers;       // CTAs (single-CTA kernel) or CTA pairs (pair kernel)
+    size_t split_bytes, sched_bytes;
+};
+
+static int gemm_plan(int64_t m, int64_t n, int64_t k_dim, bool has_bias, GemmPlan *p) {
     int dev = 0, sms = 148;
     SRUB_CUDA_CHECK(cudaGetDevice(&dev));
     SRUB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     const int64_t tiles256 = ((m + 255) / 256) * ((n + BN - 1) / BN);
     // measured: from about 32 tiles of 256 x 256 on, the pair kernel beats twice as many 128 x 256 tiles on single CTAs
     bool pair = tiles256 >= 32 && m > 160;   // a 256-row tile over at most 160 rows is mostly padding
-    if (const char *e = getenv("SRU_B200_GEMM_2SM")) pair = (*e == '1');
+    const int forced = option(OPT_GEMM_2SM, -1);
+    if (forced >= 0) pair = forced != 0;
     const int64_t tiles = pair ? tiles256 : ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
     const int nkb = (int)((k_dim + BK - 1) / BK);
-    *two_sm = pair;
-    *ksplit = has_bias ? 1 : choose_ksplit(tiles, pair ? sms / 2 : sms, nkb);
-    *tail_s = 0;
-    *tail_t0 = 0;
-    if (pair && !has_bias && *ksplit == 1) *tail_s = choose_tail_split(tiles, sms / 2, nkb, tail_t0);
+    p->two_sm = pair;
+    p->workers = pair ? sms / 2 : sms;
+    int ksplit = has_bias ? 1 : choose_ksplit(tiles, p->workers, nkb);
+    const int kbps = (nkb + ksplit - 1) / ksplit;
+    ksplit = (nkb + kbps - 1) / kbps;
+    p->ksplit = ksplit;
+    p->units = tiles * ksplit;
+    p->split_bytes = ksplit > 1 ? (size_t)ksplit * (size_t)m * (size_t)n * sizeof(float) : 0;
+    const int64_t npairs = std::min<int64_t>(p->units, p->workers);
+    p->dynamic = pair && option(OPT_GEMM_DYNAMIC, 0) != 0 && p->units > npairs && npairs <= kSchedMaxPairs;
+    p->sched_bytes = p->dynamic ? (size_t)(1 + npairs * kSchedRing) * sizeof(unsigned long long) : 0;
     return 0;
 }
 
 static int gemm_impl(void *c, const void *a, const void *b, const float *col_bias, int64_t m, int64_t n,
                      int64_t k_dim, int64_t lda, int64_t ldb, int64_t ldc, int trans_a, int trans_b,
                      int ab_dtype, int c_dtype, int accumulate, void *workspace, size_t workspace_bytes,
-                     size_t *want_bytes, void *stream) {
+                     void *stream) {
     if (m < 0 || n < 0 || k_dim < 1) return set_error(SRU_ERR_BAD_ARG, "bad gemm sizes");
     if (m == 0 || n == 0) return 0;
     if (!c || !a || !b) return set_error(SRU_ERR_BAD_ARG, "gemm pointers must not be null");
@@ -954,21 +867,23 @@ static int gemm_impl(void *c, const void *a, const void *b, const float *col_bia
     // the tensor-map encoder is a driver entry point: this thread needs the primary context
     if (int rc = ensure_context()) return rc;
 
-    // Pair kernel (two SMs per 256 x 256 tile) once there are enough such tiles to fill the GPU;
-    // SRU_B200_GEMM_2SM=0/1 overrides.  Split-K needs a caller workspace; without one it is off.
-    int dev = 0, sms = 148;
+    int dev = 0;
     SRUB_CUDA_CHECK(cudaGetDevice(&dev));
-    SRUB_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    bool two_sm = false;
-    int ksplit = 1, tail_s = 0, tail_t0 = 0;
-    if (int prc = gemm_plan(m, n, k_dim, col_bias != nullptr, &two_sm, &ksplit, &tail_s, &tail_t0)) return prc;
+    GemmPlan plan;
+    if (int prc = gemm_plan(m, n, k_dim, col_bias != nullptr, &plan)) return prc;
+    const bool two_sm = plan.two_sm;
+    // Both extras live in the caller's workspace ([K-slab partials][scheduler words]); what does not fit is
+    // simply not used: no split, static tile order.
     const int nkb_all = (int)((k_dim + BK - 1) / BK);
-    int kbps = (nkb_all + ksplit - 1) / ksplit;
-    ksplit = (nkb_all + kbps - 1) / kbps;
-    if (ksplit > 1 && (!workspace || workspace_bytes < (size_t)ksplit * m * n * sizeof(float))) {
-        ksplit = 1;
-        kbps = nkb_all;
-    }
+    int ksplit = plan.ksplit;
+    size_t ws_used = 0;
+    if (ksplit > 1 && (!workspace || workspace_bytes < plan.split_bytes)) ksplit = 1;
+    if (ksplit > 1) ws_used = (plan.split_bytes + 15) & ~size_t(15);
+    const int kbps = (nkb_all + ksplit - 1) / ksplit;
+    unsigned long long *sched = nullptr;
+    if (plan.dynamic && ksplit == plan.ksplit && workspace && workspace_bytes >= ws_used + plan.sched_bytes &&
+        (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0)
+        sched = reinterpret_cast<unsigned long long *>(static_cast<uint8_t *>(workspace) + ws_used);
 
     CUtensorMap map_a, map_b;
     int rc;
@@ -1000,27 +915,17 @@ static int gemm_impl(void *c, const void *a, const void *b, const float *col_bia
     if (!g.err) return set_error(SRU_ERR_CUDA, "device error flag unavailable");
     g.ksplit = ksplit;
     g.kbps = kbps;
-    g.tail_s = 0; g.tail_t0 = 0; g.tail_kbps = 0; g.tail_ws = nullptr;
     const int64_t tiles_all = (int64_t)g.tiles_m * g.tiles_n;
-    if (tail_s > 0) {
-        const size_t need = (size_t)(tiles_all - tail_t0) * tail_s * 65536 * sizeof(float);
-        if (workspace && workspace_bytes >= need) {
-            g.tail_s = tail_s; g.tail_t0 = tail_t0;
-            g.tail_kbps = (nkb_all + tail_s - 1) / tail_s;
-            g.tail_ws = static_cast<float *>(workspace);
-        }
-    }
     void *final_c = c;
     const int final_dtype = c_dtype, final_acc = g.accumulate;
     if (ksplit > 1) {   // partial products go to [ksplit][M][N] fp32; splitk_reduce finishes the job
         g.c = workspace; g.ldc = n; g.c_dtype = SRU_F32; g.accumulate = 0;
     }
-    const int64_t ntiles = g.tail_s > 0 ? g.tail_t0 + (tiles_all - g.tail_t0) * g.tail_s
-                                        : tiles_all * ksplit;   // work units
+    const int64_t ntiles = tiles_all * ksplit;   // work units
     if (ntiles > 0x7fffffff) return set_error(SRU_ERR_BAD_ARG, "too many gemm tiles");
 
     static bool attr_set[64] = {false};
-    if (dev < 64 && !attr_set[dev]) {
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
         SRUB_CUDA_CHECK(cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              kSmemBytes));
         SRUB_CUDA_CHECK(cudaFuncSetAttribute(gemm_tcgen05_2sm_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1031,22 +936,22 @@ static int gemm_impl(void *c, const void *a, const void *b, const float *col_bia
     }
     g.sched = nullptr;
     g.epi_warps = (nkb_all <= 16) ? 8 : 4;      // see the epilogue of the pair kernel
-    if (const char *e = getenv("SRU_B200_GEMM_EPI_WARPS")) g.epi_warps = (atoi(e) == 8) ? 8 : 4;
+    const int epi_forced = option(OPT_GEMM_EPI_WARPS, -1);
+    if (epi_forced >= 0) g.epi_warps = (epi_forced == 8) ? 8 : 4;
     if (two_sm) {
-        // Dynamic tile order (SRU_B200_GEMM_DYNAMIC=1) once there is more than one round of units.  It is meant for
+        // Dynamic tile order (option gemm_dynamic) once there is more than one round of units.  It is meant for
         // products that share the GPU with another kernel (the gradient all-reduce of data-parallel training, whose
-        // host side switches it on); alone on the GPU the static order is as fast or faster.
-        const char *dyn = getenv("SRU_B200_GEMM_DYNAMIC");
-        const int64_t npairs_l = std::min<int64_t>(ntiles, sms / 2);
-        if (dyn && atoi(dyn) != 0 && ntiles > npairs_l && npairs_l <= kSchedMaxPairs) {
-            g.sched = next_sched_set();
-            if (g.sched)
-                SRUB_CUDA_CHECK(cudaMemsetAsync(g.sched, 0xFF, (size_t)(1 + npairs_l * kSchedRing) * sizeof(unsigned long long),
-                                                static_cast<cudaStream_t>(stream)));
+        // host side switches it on); alone on the GPU the static order is as fast or faster.  Counter and mailboxes
+        // sit in the caller's workspace, so products on different streams never share them; they are refilled
+        // (0xFF) on the product's stream right before its launch.
+        const int64_t npairs_l = std::min<int64_t>(ntiles, plan.workers);
+        if (sched) {
+            g.sched = sched;
+            SRUB_CUDA_CHECK(cudaMemsetAsync(g.sched, 0xFF, plan.sched_bytes, static_cast<cudaStream_t>(stream)));
         }
         cudaLaunchConfig_t cfg;
         memset(&cfg, 0, sizeof(cfg));
-        cfg.gridDim = dim3(2u * (unsigned)std::min<int64_t>(ntiles, sms / 2), 1, 1);
+        cfg.gridDim = dim3(2u * (unsigned)npairs_l, 1, 1);
         cfg.blockDim = dim3(64 + 32 * g.epi_warps, 1, 1);
         cfg.dynamicSmemBytes = kSmemBytes2;
         cfg.stream = static_cast<cudaStream_t>(stream);
@@ -1058,24 +963,13 @@ static int gemm_impl(void *c, const void *a, const void *b, const float *col_bia
         if (g.epi_warps == 8) SRUB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tcgen05_2sm_kernel<8>, map_a, map_b, g));
         else SRUB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tcgen05_2sm_kernel<4>, map_a, map_b, g));
     } else {
-        const unsigned grid = (unsigned)std::min<int64_t>(ntiles, sms);
+        const unsigned grid = (unsigned)std::min<int64_t>(ntiles, plan.workers);
         gemm_tcgen05_kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(map_a, map_b, g);
     }
     SRUB_CUDA_CHECK(cudaGetLastError());
-    if (g.tail_s > 0) {
-        const unsigned blocks = (unsigned)((tiles_all - g.tail_t0) * 64);
-        cudaStream_t st = static_cast<cudaStream_t>(stream);
-        if (final_dtype == SRU_BF16)
-            tail_reduce<__nv_bfloat16><<<blocks, 256, 0, st>>>(g.tail_ws, g.tail_s, g.tail_t0, g.tiles_n, m, n, (__nv_bfloat16 *)final_c, ldc, final_acc);
-        else if (final_dtype == SRU_F16)
-            tail_reduce<__half><<<blocks, 256, 0, st>>>(g.tail_ws, g.tail_s, g.tail_t0, g.tiles_n, m, n, (__half *)final_c, ldc, final_acc);
-        else
-            tail_reduce<float><<<blocks, 256, 0, st>>>(g.tail_ws, g.tail_s, g.tail_t0, g.tiles_n, m, n, (float *)final_c, ldc, final_acc);
-        SRUB_CUDA_CHECK(cudaGetLastError());
-    }
     if (ksplit > 1) {
         const int64_t items = m * (n / 4);
-        const unsigned blocks = (unsigned)std::min<int64_t>((items + 255) / 256, (int64_t)sms * 8);
+        const unsigned blocks = (unsigned)std::min<int64_t>((items + 255) / 256, (int64_t)plan.workers * 16);
         cudaStream_t st = static_cast<cudaStream_t>(stream);
         const float *ws = static_cast<const float *>(workspace);
         if (final_dtype == SRU_BF16)
@@ -1093,20 +987,14 @@ extern "C" int sru_b200_gemm(void *c, const void *a, const void *b, const float 
                              int64_t k_dim, int64_t lda, int64_t ldb, int64_t ldc, int trans_a, int trans_b,
                              int ab_dtype, int c_dtype, int accumulate, void *stream) {
     return gemm_impl(c, a, b, col_bias, m, n, k_dim, lda, ldb, ldc, trans_a, trans_b, ab_dtype, c_dtype, accumulate,
-                     nullptr, 0, nullptr, stream);
+                     nullptr, 0, stream);
 }
 
 extern "C" size_t sru_b200_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k_dim, int has_bias) {
     if (m <= 0 || n <= 0 || k_dim <= 0) return 0;
-    bool two_sm = false;
-    int ksplit = 1, tail_s = 0, tail_t0 = 0;
-    if (gemm_plan(m, n, k_dim, has_bias != 0, &two_sm, &ksplit, &tail_s, &tail_t0) != 0) return 0;
-    if (tail_s > 0) {
-        const int64_t tiles = ((m + 255) / 256) * ((n + BN - 1) / BN);
-        return (size_t)(tiles - tail_t0) * tail_s * 65536 * sizeof(float);
-    }
-    if (ksplit <= 1) return 0;
-    return (size_t)ksplit * (size_t)m * (size_t)n * sizeof(float);
+    GemmPlan plan;
+    if (gemm_plan(m, n, k_dim, has_bias != 0, &plan) != 0) return 0;
+    return ((plan.split_bytes + 15) & ~size_t(15)) + plan.sched_bytes;
 }
 
 extern "C" int sru_b200_gemm_ws(void *c, const void *a, const void *b, const float *col_bias, int64_t m, int64_t n,
@@ -1114,5 +1002,5 @@ extern "C" int sru_b200_gemm_ws(void *c, const void *a, const void *b, const flo
                                 int ab_dtype, int c_dtype, int accumulate, void *workspace, size_t workspace_bytes,
                                 void *stream) {
     return gemm_impl(c, a, b, col_bias, m, n, k_dim, lda, ldb, ldc, trans_a, trans_b, ab_dtype, c_dtype, accumulate,
-                     workspace, workspace_bytes, nullptr, stream);
+                     workspace, workspace_bytes, stream);
 }

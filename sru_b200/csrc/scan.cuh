@@ -43,7 +43,6 @@ struct TileCfg {
     int nrt;       // row tiles = ceil(B / br)
     int nstages;   // ring depth
     int ss;        // time steps per ring stage (a multiple of 4)
-    int debug;     // timing experiments only: 1 = no copies, 2 = consumers only wait and release
     int v;         // columns per thread
     int threads;   // consumer threads (br * tpr, rounded up to a warp) + one producer warp
     size_t smem;   // dynamic shared memory bytes

@@ -99,14 +99,10 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const __grid_constant__ Sca
             const uint32_t bar = bar_full + 8 * s;
             const uint32_t sbase = smem_u32(stage0) + (uint32_t)s * stage_bytes;
             if (lane == 0) {
-                if (p.c.debug & 1) {
-                    mbar_arrive(bar);
-                } else {
-                    const int t0 = first_time(it);
-                    mbar_arrive_expect_tx(bar, (uint32_t)SS * BR * (u_slab + x_slab));
-                    tma_load_3d(sbase, &maps.u, bar, xu, (int)b0, t0);
-                    if (has_x) tma_load_3d(sbase + u_region, &maps.x, bar, xx, (int)b0, t0);
-                }
+                const int t0 = first_time(it);
+                mbar_arrive_expect_tx(bar, (uint32_t)SS * BR * (u_slab + x_slab));
+                tma_load_3d(sbase, &maps.u, bar, xu, (int)b0, t0);
+                if (has_x) tma_load_3d(sbase + u_region, &maps.x, bar, xx, (int)b0, t0);
             }
             if (has_pad) {
                 // this stage's flags were read from global memory one stage ago; the next stage's are
@@ -209,7 +205,7 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const __grid_constant__ Sca
             }
             const uint32_t sb = order_after_wait(smem_u32(stage0) + (uint32_t)s * stage_bytes);
             for (int q = 0; q < SS && n < L; q += kTS, n += kTS) {
-                if (active && !(p.c.debug & 2)) {
+                if (active) {
                     const int slab = asc ? q : (SS - 1 - q);
                     // the block's four flags, byte ts = scan step ts of the block
                     const uint32_t pad_cur = PADF ? pad_word(sb + pad_off, q, SS, asc) : 0u;
@@ -507,11 +503,6 @@ static int num_sms() {
     return g_num_sms;
 }
 
-static int env_int(const char *name, int dflt) {
-    const char *e = getenv(name);
-    return (e && *e) ? atoi(e) : dflt;
-}
-
 static PFN_cuTensorMapEncodeTiled_v12000 scan_encode_fn() {
     static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
     if (!fn) {
@@ -579,10 +570,10 @@ static bool choose_tile(int64_t L, int64_t B, int64_t d, int dirs, int k, int sk
         else { v = 2; ntc = 128; }
     }
     while (ntc > 32 && ncols / ((int64_t)v * ntc) < (int64_t)sms / 2) ntc /= 2;   // tiny problems: spread over the SMs
-    v = env_int(backward ? "SRU_B200_BWD_V" : "SRU_B200_FWD_V", v);
+    v = option(backward ? OPT_BWD_V : OPT_FWD_V, v);
     if (v < vmin || v > vmax || (v & (v - 1))) return false;
-    ntc = env_int("SRU_B200_SCAN_THREADS", ntc);
-    ntc = env_int(backward ? "SRU_B200_BWD_THREADS" : "SRU_B200_FWD_THREADS", ntc);
+    ntc = option(OPT_SCAN_THREADS, ntc);
+    ntc = option(backward ? OPT_BWD_THREADS : OPT_FWD_THREADS, ntc);
     if (ntc < 32 || ntc > 128 || ntc % 32) return false;
     // hidden width of the tile: largest divisor of d, multiple of the granule, <= v*ntc, and with a
     // U slab of at most 2048 bytes (256 eight-byte elements, the widest box the tensor map takes)
@@ -607,7 +598,7 @@ static bool choose_tile(int64_t L, int64_t B, int64_t d, int dirs, int k, int sk
     const size_t ring0 = std::min<size_t>(200 * 1024 / cps0, 96 * 1024);
     int ss = kTS;
     while (ss < 32 && (size_t)ss * br * per_row_step < 16 * 1024 && (size_t)(2 * ss) * br * per_row_step * 3 <= ring0) ss *= 2;
-    ss = env_int("SRU_B200_SCAN_SS", ss);
+    ss = option(OPT_SCAN_SS, ss);
     if (ss < kTS || ss > 64 || ss % kTS) return false;
     while (has_pad && br * ss > 32 * kPadPerLane) ss -= kTS;
     auto stage_size = [&](int steps) {
@@ -623,7 +614,7 @@ static bool choose_tile(int64_t L, int64_t B, int64_t d, int dirs, int k, int sk
     size_t ring = std::min<size_t>(200 * 1024 / cta_per_sm, 96 * 1024);
     int ns = (int)(ring / stage_bytes);
     ns = std::max(2, std::min(ns, kMaxStages));
-    ns = env_int("SRU_B200_SCAN_STAGES", ns);
+    ns = option(OPT_SCAN_STAGES, ns);
     ns = std::max(2, std::min(ns, kMaxStages));
     size_t smem = kBarBytes + (size_t)ns * stage_bytes;
     if (backward) smem = std::max(smem, kBarBytes + (size_t)br * 4 * hw * sizeof(float));
@@ -634,7 +625,7 @@ static bool choose_tile(int64_t L, int64_t B, int64_t d, int dirs, int k, int sk
     }
     out->hw = hw; out->br = br; out->tpr = tpr;
     out->nht = (int)(D / hw); out->nrt = (int)((B + br - 1) / br);
-    out->nstages = ns; out->ss = ss; out->v = v; out->debug = env_int("SRU_B200_SCAN_DEBUG", 0);
+    out->nstages = ns; out->ss = ss; out->v = v;
     out->threads = cthreads + 32; out->smem = smem;
     return nctas <= 0x7fffffff;
 }
@@ -644,7 +635,7 @@ static bool pipelined_eligible(const ScanArgs &a) {
     if (a.k == 3 && a.skip_type != 1) return false;   // k = 3 without a highway term: generic kernel
     if (a.k == 4 && a.skip_type != 2) return false;
     if (a.dtype == SRU_F64) return false;
-    if (env_int("SRU_B200_FORCE_GENERIC", 0)) return false;
+    if (option(OPT_FORCE_GENERIC, 0)) return false;
     return true;
 }
 
@@ -659,9 +650,16 @@ template <typename T, typename TC, int V, int K>
 static int launch_t(const ScanMaps &maps, const PipeArgs &p, bool backward, cudaStream_t st) {
     auto fwd = scan_fwd_pipe<T, TC, V, K>;
     auto bwd = scan_bwd_pipe<T, TC, V, K>;
-    const void *fn = backward ? (const void *)bwd : (const void *)fwd;
-    if (p.c.smem > 48 * 1024)
-        SRUB_CUDA_CHECK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.c.smem));
+    // the opt-in to more than 48 KB of dynamic shared memory is made once per kernel instance and device
+    static bool opted[2][64] = {{false}};
+    int dev = 0;
+    SRUB_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return set_error(SRU_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+    if (!opted[backward ? 1 : 0][dev]) {
+        const void *fn = backward ? (const void *)bwd : (const void *)fwd;
+        SRUB_CUDA_CHECK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        opted[backward ? 1 : 0][dev] = true;
+    }
     const unsigned grid = (unsigned)((int64_t)p.c.nht * p.c.nrt);
     if (backward) bwd<<<grid, p.c.threads, p.c.smem, st>>>(maps, p);
     else fwd<<<grid, p.c.threads, p.c.smem, st>>>(maps, p);
@@ -730,6 +728,7 @@ int launch_scan_pipelined(const ScanArgs &a, bool backward, cudaStream_t st) {
                                                      (int64_t)a.d * a.dirs, 1, st);
         if (r2 < 0) return r2;
     }
+    note_scan_kernel(SCAN_KERNEL_PIPELINED);
     return 1;
 }
 

@@ -7,16 +7,23 @@ dimension with nn.DataParallel in misc/test_multigpu.py:43-44); sequences are in
 nothing but the parameter gradients ever crosses ranks.
 
 ``LayerGradAllReducer`` keeps each layer's gradients in one flat bucket (``p.grad`` are views
-of it), and starts that layer's all-reduce asynchronously as soon as autograd has produced the
-last gradient of the layer, so the collective of layer i overlaps the backward of layers < i.
+of it) and all-reduces a bucket asynchronously once autograd has produced the last gradient of
+that layer, so the collective of layer i overlaps the backward of the layers below it.
 Works with any ``torch.distributed`` backend (NCCL on GPUs, gloo in the CPU tests).
+
+When the collective starts matters: a layer's bucket is complete right after its weight-gradient
+GEMM, which is exactly when the NEXT layer's backward scan begins, and both the scan and the
+all-reduce are bound by HBM bandwidth.  With ``defer_to_scan_end`` (default) a complete bucket
+is held until that next backward scan has been enqueued, so that the all-reduce overlaps the
+two tensor-bound GEMMs that follow it instead of the scan.
 """
-import os
 from typing import Dict, List, Optional
 
 import torch
 import torch.distributed as dist
 import torch.nn as nn
+
+from . import ops
 
 
 def shard_batch(t: Optional[torch.Tensor], rank: int, world: int, dim: int = 1) -> Optional[torch.Tensor]:
@@ -33,17 +40,31 @@ class LayerGradAllReducer:
     """Per-layer bucketed gradient all-reduce (SUM) overlapped with backward.
 
     groups: list of lists of parameters; by default one group per child of ``model.rnn_lst``
-    plus one group for whatever is left.  Call ``finish()`` after ``backward()`` and before the
-    gradients are read.
+    plus one group for whatever is left.
+
+    Protocol per step: zero the gradients (``reducer.zero_grad()``, or any optimizer's
+    ``zero_grad`` -- with ``set_to_none=True`` the next backward's fresh gradient tensors are copied
+    into the buckets and re-bound as views), run ONE ``backward()``, call ``finish()``, read the
+    gradients.  ``finish()`` all-reduces every bucket that backward did not complete (a layer with
+    a parameter that received no gradient), waits for all of them and re-arms the reducer.  A second
+    ``backward()`` before ``finish()`` raises: its gradients would be added to sums that other ranks
+    have already reduced.
+
+    reduce_dtype: all-reduce a copy of the bucket in this dtype (e.g. ``torch.bfloat16``: half the
+    bytes on the wire and in HBM) and write the result back into the fp32 bucket; ``None`` reduces
+    the bucket itself.
+    dynamic_gemm_order: switch the pair GEMM of this package to its dynamic tile order (option
+    ``gemm_dynamic``), which keeps a product from waiting on the CTA pairs whose SMs the
+    collective held for a while.  Only touched when the world size is above one and the
+    parameters live on a GPU.
     """
 
-    def __init__(self, model: nn.Module, process_group=None, groups: Optional[List[List[nn.Parameter]]] = None):
+    def __init__(self, model: nn.Module, process_group=None, groups: Optional[List[List[nn.Parameter]]] = None,
+                 reduce_dtype: Optional[torch.dtype] = None, defer_to_scan_end: bool = True,
+                 dynamic_gemm_order: bool = True):
         self.group = process_group
         self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
-        if self.world > 1:
-            # the all-reduces run next to backward and take SMs from it for a while: let the persistent GEMM hand
-            # out its tiles dynamically so that pairs that start late simply take fewer (explicit settings win)
-            os.environ.setdefault("SRU_B200_GEMM_DYNAMIC", "1")
+        self.reduce_dtype = reduce_dtype
         if groups is None:
             groups = []
             seen = set()
@@ -57,48 +78,136 @@ class LayerGradAllReducer:
                 groups.append(rest)
         self.groups = groups
         self.buckets: List[torch.Tensor] = []
-        self._pending: List[int] = []
-        self._handles = []
+        self._views: Dict[int, torch.Tensor] = {}      # id(param) -> its slice of the bucket, shaped like the param
         self._index: Dict[int, int] = {}
+        self._seen: List[set] = []
+        self._launched: List[bool] = []
+        self._ready: List[int] = []                     # complete buckets waiting for the next scan backward
+        self._handles = []                              # (work handle, bucket index, reduced copy or None)
         self._hooks = []
+        on_gpu = False
         for gi, ps in enumerate(groups):
             total = sum(p.numel() for p in ps)
             flat = torch.zeros(total, dtype=ps[0].dtype, device=ps[0].device)
+            on_gpu = on_gpu or flat.is_cuda
             off = 0
             for p in ps:
                 if p.dtype != flat.dtype:
                     raise ValueError("all parameters of a bucket must share one dtype")
-                p.grad = flat[off:off + p.numel()].view_as(p)
+                view = flat[off:off + p.numel()].view_as(p)
+                self._views[id(p)] = view
+                p.grad = view
                 off += p.numel()
                 self._index[id(p)] = gi
                 self._hooks.append(p.register_post_accumulate_grad_hook(self._on_grad))
             self.buckets.append(flat)
-            self._pending.append(len(ps))
+            self._seen.append(set())
+            self._launched.append(False)
+        self._defer = bool(defer_to_scan_end) and self.world > 1
+        if self._defer:
+            ops.add_scan_backward_listener(self._after_scan_backward)
+        if self.world > 1 and on_gpu and dynamic_gemm_order:
+            from . import _lib
+            if _lib.get_option("gemm_dynamic") < 0:      # an explicit setting wins
+                _lib.set_option("gemm_dynamic", 1)
 
+    # ------------------------------------------------------------------ per step
     def zero_grad(self):
-        """Zeroes the buckets in place (gradients stay views of them) and re-arms the counters."""
+        """Zeroes the buckets in place and binds every ``p.grad`` to its slice again."""
         for gi, flat in enumerate(self.buckets):
             flat.zero_()
-            self._pending[gi] = len(self.groups[gi])
+            for p in self.groups[gi]:
+                if p.grad is not self._views[id(p)]:
+                    p.grad = self._views[id(p)]
+        self._rearm()
+
+    def _rearm(self):
+        for gi in range(len(self.buckets)):
+            self._seen[gi].clear()
+            self._launched[gi] = False
+        self._ready = []
         self._handles = []
 
     def _on_grad(self, p: torch.Tensor):
         gi = self._index[id(p)]
-        self._pending[gi] -= 1
-        if self._pending[gi] == 0 and self.world > 1:
-            self._handles.append(dist.all_reduce(self.buckets[gi], op=dist.ReduceOp.SUM, group=self.group,
-                                                 async_op=True))
+        if self._launched[gi] or id(p) in self._seen[gi]:
+            raise RuntimeError(
+                "LayerGradAllReducer: a parameter received a second gradient before finish(); run one "
+                "backward() per step and call finish() after it")
+        view = self._views[id(p)]
+        g = p.grad
+        if g is not view and not (g is not None and g.data_ptr() == view.data_ptr() and g.dtype == view.dtype
+                                  and g.shape == view.shape and g.is_contiguous()):
+            # the gradient was detached from its bucket (zero_grad(set_to_none=True), an optimizer that
+            # replaced it): this step's value is in the fresh tensor; put it into the bucket and re-bind
+            with torch.no_grad():
+                view.copy_(g)
+            p.grad = view
+        self._seen[gi].add(id(p))
+        if len(self._seen[gi]) == len(self.groups[gi]):
+            if self._defer:
+                self._ready.append(gi)
+            else:
+                self._launch(gi)
+
+    def _after_scan_backward(self):
+        """Called right after a backward scan has been enqueued: the buckets completed before it start now."""
+        ready, self._ready = self._ready, []
+        for gi in ready:
+            self._launch(gi)
+
+    def _launch(self, gi: int):
+        if self._launched[gi]:
+            return
+        self._launched[gi] = True
+        if self.world <= 1:
+            return
+        flat = self.buckets[gi]
+        if self.reduce_dtype is not None and self.reduce_dtype != flat.dtype:
+            wire = flat.to(self.reduce_dtype)
+            h = dist.all_reduce(wire, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+            self._handles.append((h, gi, wire))
+        else:
+            h = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+            self._handles.append((h, gi, None))
 
     def finish(self):
-        """Waits for every all-reduce started during backward (stream-ordered for NCCL)."""
-        for h in self._handles:
+        """Starts what backward left (in bucket order, the same on every rank), waits for every all-reduce
+        (stream-ordered for NCCL) and re-arms the reducer for the next step."""
+        for gi in self._ready:
+            self._launch(gi)
+        self._ready = []
+        for gi in range(len(self.buckets)):
+            if not self._launched[gi]:
+                # a parameter of this layer got no gradient this step: its slice holds what zero_grad left
+                for p in self.groups[gi]:
+                    if id(p) not in self._seen[gi] and p.grad is not self._views[id(p)]:
+                        if p.grad is not None:
+                            with torch.no_grad():
+                                self._views[id(p)].copy_(p.grad)
+                        p.grad = self._views[id(p)]
+                self._launch(gi)
+        for h, gi, wire in self._handles:
             h.wait()
-        self._handles = []
+            if wire is not None:
+                self.buckets[gi].copy_(wire)
+        self._rearm()
 
+    # ------------------------------------------------------------------ misc
     def bytes_per_step(self) -> int:
-        return sum(b.numel() * b.element_size() for b in self.buckets)
+        """Bytes handed to the collective per step."""
+        total = 0
+        for b in self.buckets:
+            size = b.element_size()
+            if self.reduce_dtype is not None:
+                size = torch.empty((), dtype=self.reduce_dtype).element_size()
+            total += b.numel() * size
+        return total
 
     def remove(self):
         for h in self._hooks:
             h.remove()
         self._hooks = []
+        if self._defer:
+            ops.remove_scan_backward_listener(self._after_scan_backward)
+            self._defer = False

@@ -164,6 +164,7 @@ class SRUCell(nn.Module):
             self.bias.zero_()
             self.bias[D:].fill_(hb)
             self.scale_x[0] = highway_scale if (self.rescale and self.has_skip_term) else 1.0
+            ops.forget_scale(self.scale_x)
 
             gates = None
             if self.custom_m is None:
@@ -201,6 +202,10 @@ class SRUCell(nn.Module):
                 if gates is not None:
                     gates[..., 1].mul_(0.5 ** 0.5)
                     gates[..., 2].mul_(0.5 ** 0.5)
+
+    def _load_from_state_dict(self, *args, **kwargs):
+        super()._load_from_state_dict(*args, **kwargs)
+        ops.forget_scale(self.scale_x)
 
     def forward(self, input: Tensor, c0: Optional[Tensor] = None,
                 mask_pad: Optional[Tensor] = None) -> Tuple[Tensor, Tensor]:

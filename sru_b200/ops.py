@@ -47,6 +47,22 @@ def set_c_hist_dtype(kind: str) -> None:
     _c_hist_dtype = kind
 
 
+# Callables invoked (no arguments) right after a backward scan has been enqueued on the current stream.  The
+# gradient all-reducer of distributed.py uses this to start a finished layer's collective behind the next
+# layer's scan instead of beside it.
+_scan_backward_listeners: list = []
+
+
+def add_scan_backward_listener(fn) -> None:
+    if fn not in _scan_backward_listeners:
+        _scan_backward_listeners.append(fn)
+
+
+def remove_scan_backward_listener(fn) -> None:
+    if fn in _scan_backward_listeners:
+        _scan_backward_listeners.remove(fn)
+
+
 def _small_dtype(storage: torch.dtype) -> torch.dtype:
     return torch.float64 if storage == torch.float64 else torch.float32
 
@@ -149,19 +165,32 @@ def _prep_small(t: Optional[Tensor], dtype: torch.dtype) -> Optional[Tensor]:
 
 def _scale_value(scale_x: Optional[Tensor]) -> float:
     """The scalar the kernels take for ``scale_x`` (sru/cuda_functional.py:73-78).  Reading a device tensor
-    synchronises the stream, so the value is remembered on the tensor object together with the tensor's
-    version counter and read again only after an in-place change (load_state_dict, reset_parameters)."""
+    synchronises the stream, so the value is remembered on the tensor object, keyed by the tensor's storage
+    address and version counter, and read again after any in-place change autograd can see (``copy_``,
+    ``fill_``, indexing assignment, ``load_state_dict``).  A write through ``.data`` does not move the version
+    counter: ``SRUCell`` drops the remembered value in ``reset_parameters`` and when a state dict is loaded,
+    and code that pokes ``scale_x.data`` itself calls ``forget_scale(scale_x)`` afterwards."""
     if scale_x is None:
         return 1.0
+    key = (scale_x.data_ptr(), scale_x._version)
     cached = getattr(scale_x, "_sru_b200_scalar", None)
-    if cached is not None and cached[0] == scale_x._version:
+    if cached is not None and cached[0] == key:
         return cached[1]
     value = float(scale_x.reshape(-1)[0])
     try:
-        scale_x._sru_b200_scalar = (scale_x._version, value)
+        scale_x._sru_b200_scalar = (key, value)
     except Exception:       # tensors that refuse attributes are simply read every time
         pass
     return value
+
+
+def forget_scale(scale_x: Optional[Tensor]) -> None:
+    """Drops the remembered scalar of ``scale_x`` (call after writing to it through ``.data``)."""
+    if scale_x is not None and hasattr(scale_x, "_sru_b200_scalar"):
+        try:
+            del scale_x._sru_b200_scalar
+        except Exception:
+            pass
 
 
 class ElementwiseRecurrence(Function):
@@ -212,6 +241,8 @@ class ElementwiseRecurrence(Function):
         grad_u, grad_x, grad_wc, grad_bias, grad_init = scan_backward(
             u.view(length, batch, D * k), x, wc, bias, init, mask_c, pad, c_hist, gh, gl,
             length, batch, d, dirs, k, act, skip_type, is_custom, scale)
+        for fn in tuple(_scan_backward_listeners):
+            fn()
         grad_u = grad_u.view(u_shape)
         if grad_x is not None:
             if ctx.link is not None:

@@ -18,9 +18,19 @@ from . import _lib
 _SIXTEEN = (torch.float16, torch.bfloat16)
 
 
+_backend = os.environ.get("SRU_B200_GEMM", "tcgen05")     # read once, at import
+
+
 def gemm_backend() -> str:
-    """'tcgen05' (default) or 'library' (SRU_B200_GEMM=library forces torch.mm everywhere)."""
-    return os.environ.get("SRU_B200_GEMM", "tcgen05")
+    """'tcgen05' (default) or 'library' (torch.mm everywhere; for A/B measurements)."""
+    return _backend
+
+
+def set_gemm_backend(name: str) -> None:
+    global _backend
+    if name not in ("tcgen05", "library"):
+        raise ValueError("gemm backend must be 'tcgen05' or 'library'")
+    _backend = name
 
 
 def _tma_compatible(x: Tensor, w: Tensor) -> bool:
@@ -61,7 +71,7 @@ def gemm(a: Tensor, b: Tensor, trans_a: bool = False, trans_b: bool = False,
         ws_bytes = int(L.sru_b200_gemm_workspace_bytes(m, n, kd, 0 if bias is None else 1))
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device) if ws_bytes else None
         _lib.call(
-            name, 2 if ws_bytes else 1, L.sru_b200_gemm_ws,
+            name, 2 if ws_bytes > 32768 else 1, L.sru_b200_gemm_ws,   # K slabs add a reduction kernel
             _lib.ptr(out), _lib.ptr(a), _lib.ptr(b), _lib.ptr(bias), m, n, kd,
             a.stride(0), b.stride(0), out.stride(0), int(trans_a), int(trans_b),
             _lib.DTYPE_CODE[a.dtype], _lib.DTYPE_CODE[out.dtype], int(accumulate),

@@ -43,3 +43,36 @@ def regression_case():
 @pytest.fixture(scope="session")
 def layer_norm_cases():
     return torch.load(os.path.join(GOLDEN, "layer_norm_cases.pt"), weights_only=False)
+
+
+@pytest.fixture
+def host_on_cpu(monkeypatch):
+    """Lets the shipped SRU / SRUCell host code run on CPU tensors, for this test only: the three device
+    operations it calls are replaced by CPU ones (torch.mm, the oracle layer norm, the oracle scan).
+    The package itself never routes anywhere but to its CUDA library."""
+    from oracle import sru_oracle
+    from sru_b200 import modules
+
+    def real_of(t):
+        return torch.float64 if t.dtype == torch.float64 else torch.float32
+
+    def recurrence(U, x, V, bias, c0, act, d, bi, skip, scale=None, mask_c=None, mask_pad=None, amp16=False,
+                   grad_link=None):
+        dt = real_of(U)
+        h, c = sru_oracle.elementwise_recurrence_oracle(
+            U.to(dt), x.to(dt), V.to(dt), bias.to(dt), c0.to(dt), act, d, bi, skip,
+            None if scale is None else scale.to(dt), None if mask_c is None else mask_c.to(dt), mask_pad)
+        return [h, c]
+
+    def project(x, w, col_bias=None, link=None):
+        out = x.mm(w)
+        return out if col_bias is None else out + col_bias.to(out.dtype)
+
+    def layer_norm(t, w, b, eps=1e-5, out_dtype=None):
+        return sru_oracle.layer_norm_oracle(t.to(real_of(t)), w, b, eps)
+
+    monkeypatch.setattr(modules.ops, "elementwise_recurrence_gpu", recurrence)
+    monkeypatch.setattr(modules, "project", project)
+    monkeypatch.setattr(modules, "layer_norm", layer_norm)
+    monkeypatch.setattr(modules, "grad_link_enabled", lambda: False)
+    return modules

@@ -96,9 +96,10 @@ def test_gemm_many_tiles_persistent():
 
 def test_projection_autograd_matches_library():
     """project() (tcgen05 forward / dgrad / wgrad) against torch.mm autograd on the same bf16 data."""
-    import os
+    from sru_b200 import projection
     from sru_b200.projection import project
-    os.environ["SRU_B200_GEMM"] = "tcgen05"
+    before = projection.gemm_backend()
+    projection.set_gemm_backend("tcgen05")
     try:
         g = torch.Generator().manual_seed(8)
         x = torch.randn(384, 256, generator=g).bfloat16().to(DEV).requires_grad_(True)
@@ -112,72 +113,35 @@ def test_projection_autograd_matches_library():
         ur.backward(gu.float())
         assert rel_err(u, ur) <= 1e-2 and rel_err(x.grad, xr.grad) <= 1e-2 and rel_err(w.grad, wr.grad) <= 1e-2
     finally:
-        os.environ.pop("SRU_B200_GEMM", None)
+        projection.set_gemm_backend(before)
 
 
-@pytest.mark.parametrize("force", [None, "4"])
+@pytest.mark.parametrize("force", [None, 4])
 def test_gemm_split_k(force):
     """Weight-gradient shape that under-fills the GPU (narrow input layer, long reduction): the K slabs'
     fp32 partials plus the reduction kernel must give the same product; also with accumulation."""
-    import os
+    from sru_b200 import _lib
     gemm = _gemm()
     g = torch.Generator().manual_seed(21)
     M, N, K = 120, 1024, 8192
     a = (torch.randn(K, M, generator=g) * 0.1).bfloat16().to(DEV)
     b = (torch.randn(K, N, generator=g) * 0.1).bfloat16().to(DEV)
     ref = a.float().t() @ b.float()
-    if force:
-        os.environ["SRU_B200_GEMM_KSPLIT"] = force
-    try:
+    with _lib.options(gemm_ksplit=force):
         out = gemm(a, b, trans_a=True, out_dtype=torch.float32)
         out16 = gemm(a, b, trans_a=True)
         base = torch.randn(M, N, generator=g).to(DEV)
         acc = base.clone()
         gemm(a, b, trans_a=True, out=acc, accumulate=True)
-    finally:
-        os.environ.pop("SRU_B200_GEMM_KSPLIT", None)
     assert rel_err(out, ref) <= 1e-4 and rel_err(out16, ref) <= 1e-2 and rel_err(acc, ref + base) <= 1e-4
-
-
-@pytest.mark.parametrize("mn", [(2048, 6144), (2000, 6136)])
-def test_gemm_tail_split(mn):
-    """A product with few rounds of tiles on the persistent grid (192 tiles of 256 x 256 on 74 CTA pairs): the tiles
-    of the last, partly filled round are cut into K slabs (fp32 partial tiles in the caller's workspace, summed by a
-    second kernel).  Same product as without the split, also for ragged edges, fp32 output and accumulation."""
-    import os
-    from sru_b200 import _lib
-    gemm = _gemm()
-    M, N = mn
-    K = 8192
-    g = torch.Generator().manual_seed(33)
-    a = (torch.randn(K, M, generator=g) * 0.1).bfloat16().to(DEV)     # weight-gradient layout: x^T grad_U
-    b = (torch.randn(K, N, generator=g) * 0.1).bfloat16().to(DEV)
-    ref = a.float().t() @ b.float()
-    assert _lib.lib().sru_b200_gemm_workspace_bytes(M, N, K, 0) == 0          # the split is opt-in
-    plain32 = gemm(a, b, trans_a=True, out_dtype=torch.float32)
-    os.environ["SRU_B200_GEMM_TAIL"] = "1"
-    try:
-        assert _lib.lib().sru_b200_gemm_workspace_bytes(M, N, K, 0) > 0
-        out32 = gemm(a, b, trans_a=True, out_dtype=torch.float32)
-        out16 = gemm(a, b, trans_a=True)
-        base = torch.randn(M, N, generator=g).to(DEV)
-        acc = base.clone()
-        gemm(a, b, trans_a=True, out=acc, accumulate=True)
-    finally:
-        os.environ.pop("SRU_B200_GEMM_TAIL", None)
-    torch.cuda.synchronize()
-    _lib.check_device_error()
-    assert rel_err(out32, ref) <= 1e-4 and rel_err(out16, ref) <= 1e-2 and rel_err(acc, ref + base) <= 1e-4
-    assert rel_err(out32, plain32) <= 1e-5
 
 
 @pytest.mark.parametrize("layout", ["nn", "nt", "tn"])
 @pytest.mark.parametrize("size", [(4096, 3072, 1024), (256 * 37, 256 * 9, 320), (2048, 6144, 64), (1000, 6144, 2048)])
 def test_gemm_dynamic_tile_order(size, layout):
-    """SRU_B200_GEMM_DYNAMIC=1: the CTA pairs take their tiles from a global counter (posted through a mailbox to
+    """Option gemm_dynamic: the CTA pairs take their tiles from a global counter (posted through a mailbox to
     both CTAs and all roles) instead of a fixed stride.  Same results, bit for bit: a tile is computed whole by
     whichever pair takes it.  Shapes with many rounds, with one k-block per tile, and with ragged edges."""
-    import os
     from sru_b200 import _lib
     gemm = _gemm()
     M, N, K = size
@@ -186,13 +150,14 @@ def test_gemm_dynamic_tile_order(size, layout):
     a = (torch.randn((K, M) if ta else (M, K), generator=g) * 0.5).bfloat16().to(DEV)
     b = (torch.randn((N, K) if tb else (K, N), generator=g) * 0.5).bfloat16().to(DEV)
     static = gemm(a, b, trans_a=ta, trans_b=tb)
-    os.environ["SRU_B200_GEMM_DYNAMIC"] = "1"
-    try:
+    assert _lib.lib().sru_b200_gemm_workspace_bytes(M, N, K, 0) == 0
+    with _lib.options(gemm_dynamic=1):
+        # counter and mailboxes live in the caller's workspace: a product with several rounds of tiles asks for it
+        if ((M + 255) // 256) * ((N + 255) // 256) > 74:
+            assert _lib.lib().sru_b200_gemm_workspace_bytes(M, N, K, 0) > 0
         for _ in range(3):       # several launches: the scheduler words are refilled per launch
             dyn = gemm(a, b, trans_a=ta, trans_b=tb)
             dyn32 = gemm(a, b, trans_a=ta, trans_b=tb, out_dtype=torch.float32)
-    finally:
-        os.environ.pop("SRU_B200_GEMM_DYNAMIC", None)
     torch.cuda.synchronize()
     _lib.check_device_error()
     assert torch.equal(dyn, static)

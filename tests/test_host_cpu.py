@@ -1,5 +1,6 @@
-"""CPU-only checks: the host-side mirror against the reference's golden vectors (through the
-oracle scan), the library's exported symbols, and argument validation that needs no GPU."""
+"""CPU-only checks of the shipped host code: SRU / SRUCell against the reference's golden vectors (with the
+three device operations replaced, for the test, by CPU ones: see the ``host_on_cpu`` fixture), the
+library's exported symbols, and argument validation that needs no GPU."""
 import ctypes
 import os
 import re
@@ -8,7 +9,6 @@ import pytest
 import torch
 
 from conftest import ROOT, rel_err
-from oracle.cpu_model import to_oracle
 from sru_b200 import _lib
 from sru_b200.modules import SRU, SRUCell
 
@@ -17,7 +17,7 @@ def _build(case):
     model = SRU(**case["kwargs"])
     missing = model.load_state_dict(case["state"], strict=True)
     assert not missing.missing_keys and not missing.unexpected_keys
-    return to_oracle(model)
+    return model
 
 
 def test_state_dict_layout_and_init_match_reference(model_cases):
@@ -35,7 +35,7 @@ def test_state_dict_layout_and_init_match_reference(model_cases):
             assert torch.equal(sd[k], v), k
 
 
-def test_model_cases_through_oracle(model_cases):
+def test_model_cases_host_code_on_cpu(model_cases, host_on_cpu):
     """Layer plumbing (LN placement, residual, c0 split, projection, compat return) is the reference's."""
     for case in model_cases:
         model = _build(case)
@@ -56,12 +56,11 @@ def test_model_cases_through_oracle(model_cases):
                     assert rel_err(p.grad, ref) <= 2e-5, (case["name"], n)
 
 
-def test_regression_artifact_through_oracle(regression_case):
+def test_regression_artifact_host_code_on_cpu(regression_case, host_on_cpu):
     """The reference's own regression vector (sru 2.3.5): outputs within 1e-6."""
     rc = regression_case
     model = SRU(**rc["kwargs"]).eval()
     model.load_state_dict(rc["state"], strict=True)
-    model = to_oracle(model).eval()
     with torch.enable_grad():
         h, c = model(rc["x"])
     assert (h - rc["h"]).abs().max() <= 1e-6

@@ -84,3 +84,77 @@ def test_oracle_layer_norm_matches_reference(layer_norm_cases, dtype, tol):
         assert rel_err(dx.view_as(case["dx"]), case["dx"]) <= tol, case["n"]
         assert rel_err(dg, case["dweight"]) <= tol, case["n"]
         assert rel_err(db, case["dbias"]) <= tol, case["n"]
+
+
+# ---------------------------------------------------------------------------------------------------------
+# The model-level checker (oracle/ref_model.py: an independent restatement of the reference's layer stack)
+# ---------------------------------------------------------------------------------------------------------
+def test_oracle_model_matches_reference_model(model_cases):
+    """OracleSRU with the reference's state dict against the reference's own sru.SRU on CPU: outputs, last
+    states and every parameter gradient (LN before / after, residual, c0 split, low-rank chain, input
+    projection, nn.RNN-style return, no-skip + tanh)."""
+    from oracle.ref_model import from_state
+    for case in model_cases:
+        model = from_state(case["kwargs"], case["state"]).train()
+        h, c = model(case["x"], case["c0"], mask_pad=case["mask_pad"])
+        (h.sum() if case["loss"] == "sum" else (h ** 2).mean()).backward()
+        assert (h - case["h"]).abs().max() <= 1e-5, case["name"]
+        assert (c - case["c"]).abs().max() <= 1e-5, case["name"]
+        grads = dict(model.named_parameters())
+        assert set(case["grads"]) <= set(grads), case["name"]
+        for n, ref in case["grads"].items():
+            g = grads[n].grad
+            # norm after the recurrence + loss h.sum(): gradients upstream of the norm are exactly zero and the
+            # reference holds rounding noise there; judge those by absolute difference
+            if float(ref.abs().max()) < 1e-6:
+                assert float((g - ref).abs().max()) <= 1e-6, (case["name"], n)
+            else:
+                assert rel_err(g, ref) <= 2e-5, (case["name"], n)
+
+
+def test_oracle_model_regression_artifact(regression_case):
+    """The reference's own regression vector (sru 2.3.5, test/regression/test_regression.py:19-51), 1e-6."""
+    from oracle.ref_model import from_state
+    rc = regression_case
+    model = from_state(rc["kwargs"], rc["state"]).eval()
+    h, c = model(rc["x"])
+    assert (h - rc["h"]).abs().max() <= 1e-6
+    assert (c - rc["c"]).abs().max() <= 1e-6
+
+
+def test_oracle_model_init_is_the_references(model_cases):
+    """Same seed, same draws: OracleSRU's initialisation reproduces the reference's reset_parameters."""
+    from oracle.ref_model import OracleSRU
+    case = [c for c in model_cases if c["name"] == "config1"][0]
+    kw = dict(case["kwargs"])
+    torch.manual_seed(0)
+    model = OracleSRU(kw.pop("input_size"), kw.pop("hidden_size"), **kw)
+    sd = model.state_dict()
+    assert list(sd.keys()) == list(case["state"].keys())
+    for k, v in case["state"].items():
+        assert torch.equal(sd[k], v), k
+
+
+@pytest.mark.parametrize("kw", [
+    dict(input_size=12, hidden_size=8, num_layers=3, bidirectional=True, layer_norm=True, rescale=True, dropout=0.2),
+    dict(input_size=16, hidden_size=16, num_layers=2, projection_size=4, highway_bias=-3.0),
+    dict(input_size=6, hidden_size=8, num_layers=2, proj_input_to_hidden_first=True, rnn_dropout=0.1,
+         weight_c_init=0.5, normalize_after=True, layer_norm=True),
+    dict(input_size=8, hidden_size=8, num_layers=2, v1=True, has_skip_term=False, use_tanh=True),
+])
+def test_oracle_model_and_shipped_model_initialise_alike(kw):
+    """Two independent statements of the reference's recipe (the checker's and the shipped host code's) draw the
+    same numbers from the same seed, for every branch of the recipe."""
+    import warnings
+    from oracle.ref_model import OracleSRU
+    from sru_b200.modules import SRU
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        torch.manual_seed(5)
+        a = SRU(**kw).state_dict()
+        torch.manual_seed(5)
+        k2 = dict(kw)
+        b = OracleSRU(k2.pop("input_size"), k2.pop("hidden_size"), **k2).state_dict()
+    assert list(a.keys()) == list(b.keys())
+    for k in a:
+        assert torch.equal(a[k], b[k]), k

@@ -4,8 +4,6 @@ Tolerances (relative to the largest magnitude of the reference tensor):
   fp64 1e-10, fp32 1e-5, bf16 / fp16 2e-2.
 For 16-bit storage the oracle runs in fp32 on the same 16-bit-rounded inputs.
 """
-import os
-
 import pytest
 import torch
 
@@ -22,20 +20,9 @@ def _ops():
     return ops
 
 
-class _env:
-    def __init__(self, **kw):
-        self.kw = {k: str(v) for k, v in kw.items() if v is not None}
-
-    def __enter__(self):
-        self.old = {k: os.environ.get(k) for k in self.kw}
-        os.environ.update(self.kw)
-
-    def __exit__(self, *a):
-        for k, v in self.old.items():
-            if v is None:
-                os.environ.pop(k, None)
-            else:
-                os.environ[k] = v
+def _opts(**kw):
+    from sru_b200 import _lib
+    return _lib.options(**kw)
 
 
 def run_both(case_inputs, dtype, c_dtype=None, need_grad=True):
@@ -166,7 +153,7 @@ def random_inputs(L, B, d, dirs, k, skip=None, pad=None, maskc=True, c0=True, sc
 @pytest.mark.parametrize("force_generic", [0, 1])
 def test_golden_cases(op_cases, dtype, force_generic):
     """Golden vectors of the reference's elementwise_recurrence_naive, outputs and all gradients."""
-    with _env(SRU_B200_FORCE_GENERIC=force_generic):
+    with _opts(force_generic=force_generic):
         for case in op_cases:
             inp = golden_inputs(case)
             out, _ = run_both(inp, dtype)
@@ -212,8 +199,7 @@ def test_pipelined_tilings(v, threads, stages):
             continue
         for (L, B, d, dirs, k, pad) in [(11, 5, 64, 2, 3, "tail"), (6, 3, 128, 1, 4, "random")]:
             inp = random_inputs(L, B, d, dirs, k, pad=pad, seed=v * 7 + threads)
-            with _env(SRU_B200_FWD_V=v, SRU_B200_BWD_V=v, SRU_B200_SCAN_THREADS=threads,
-                      SRU_B200_SCAN_STAGES=stages):
+            with _opts(fwd_v=v, bwd_v=v, scan_threads=threads, scan_stages=stages):
                 out, ref = run_both(inp, dtype)
             compare(out, ref, TOL[dtype], (v, threads, stages, dtype, L, B, d, dirs, k))
 
@@ -226,12 +212,10 @@ def test_pad_flags_across_stages(v, threads, ss):
     short of rows), both directions, random and tail padding."""
     for pad in ("random", "tail"):
         inp = random_inputs(71, 7, 64, 2, 3, pad=pad, seed=ss + v)
-        with _env(SRU_B200_FWD_V=v, SRU_B200_BWD_V=v, SRU_B200_SCAN_THREADS=threads,
-                  SRU_B200_SCAN_STAGES=2, SRU_B200_SCAN_SS=ss):
+        with _opts(fwd_v=v, bwd_v=v, scan_threads=threads, scan_stages=2, scan_ss=ss):
             out, ref = run_both(inp, torch.bfloat16)
         compare(out, ref, TOL[torch.bfloat16], (v, threads, ss, pad))
-        with _env(SRU_B200_FWD_V=min(v, 2), SRU_B200_BWD_V=v, SRU_B200_SCAN_THREADS=threads,
-                  SRU_B200_SCAN_STAGES=3, SRU_B200_SCAN_SS=ss):
+        with _opts(fwd_v=min(v, 2), bwd_v=v, scan_threads=threads, scan_stages=3, scan_ss=ss):
             out, ref = run_both(inp, torch.float32)
         compare(out, ref, TOL[torch.float32], (v, threads, ss, pad, "fp32"))
 
