@@ -170,8 +170,11 @@ int sru_b200_scan_backward(
  *   - All calls on a device share the one array.  Nothing in it needs clearing between
  *     calls, but two calls whose kernels overlap on the GPU (different streams without
  *     an ordering between them) race on it: keep calls on one device stream-ordered.
- *   - No cudaMalloc / cudaFree, no allocating library routine, inputs and outputs are
- *     still the caller's.
+ *   - No cudaMalloc, no allocating library routine; inputs and outputs are still the caller's.
+ *     One exception to "no runtime memory call at all": on a host thread that has no CUDA context
+ *     bound yet, the library binds the device's primary context with cudaFree(NULL), which frees
+ *     nothing and allocates nothing; a thread that already has a context (any thread that has made
+ *     a runtime call on this device) never reaches it.
  */
 size_t sru_b200_scan_backward_noalloc_max_bytes(void);
 
@@ -207,6 +210,16 @@ int sru_b200_gemm(
     int64_t m, int64_t n, int64_t k_dim,
     int64_t lda, int64_t ldb, int64_t ldc,
     int trans_a, int trans_b, int ab_dtype, int c_dtype, int accumulate, void *stream);
+
+/*
+ * Lays the layer's gate bias out as the col_bias vector of the projection above, so that the GEMM's
+ * epilogue adds it to U and the scan runs with bias = NULL.  `bias` is the layer's parameter, float
+ * (2, width) with width = dirs * d (sru/modules.py:150; index map sru_cuda_kernel.cu:47-51);
+ * `col_bias` receives float[width * k]: bias[0][j] at column j*k + 1, bias[1][j] at column j*k + 2, zeros
+ * at the candidate column j*k and (k = 4) the highway column j*k + 3.  grad_bias still comes from the
+ * backward scan (the column sums of grad_U at those columns are what it accumulates, :148,:156).
+ */
+int sru_b200_gate_bias_columns(float *col_bias, const float *bias, int64_t width, int k, void *stream);
 
 /*
  * The same contraction with caller-provided scratch.  Products whose output tiles alone

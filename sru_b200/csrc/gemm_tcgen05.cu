@@ -983,6 +983,27 @@ static int gemm_impl(void *c, const void *a, const void *b, const float *col_bia
     return 0;
 }
 
+// Gate bias (2, D) -> per-column vector of U's gate-innermost layout: column (j*k + 1) gets bias[0][j], column
+// (j*k + 2) gets bias[1][j], the candidate (and highway) columns get 0.
+__global__ void gate_bias_columns_kernel(float *__restrict__ out, const float *__restrict__ bias, int64_t D, int k) {
+    const int64_t n = D * k;
+    for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < n; c += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t j = c / k;
+        const int g = (int)(c - j * k);
+        out[c] = (g == 1) ? bias[j] : (g == 2) ? bias[D + j] : 0.f;
+    }
+}
+
+extern "C" int sru_b200_gate_bias_columns(float *col_bias, const float *bias, int64_t width, int k, void *stream) {
+    if (!col_bias || !bias || width < 1 || (k != 3 && k != 4))
+        return set_error(SRU_ERR_BAD_ARG, "gate_bias_columns: null pointer, width < 1 or k not 3 / 4");
+    const int64_t n = width * k;
+    const unsigned blocks = (unsigned)std::min<int64_t>((n + 255) / 256, 1024);
+    gate_bias_columns_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(col_bias, bias, width, k);
+    SRUB_CUDA_CHECK(cudaGetLastError());
+    return 0;
+}
+
 extern "C" int sru_b200_gemm(void *c, const void *a, const void *b, const float *col_bias, int64_t m, int64_t n,
                              int64_t k_dim, int64_t lda, int64_t ldb, int64_t ldc, int trans_a, int trans_b,
                              int ab_dtype, int c_dtype, int accumulate, void *stream) {

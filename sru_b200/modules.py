@@ -21,7 +21,8 @@ from torch.nn.utils.rnn import PackedSequence
 from . import _lib
 from . import ops
 from .layer_norm import layer_norm
-from .projection import GradLink, gemm_backend, grad_link_enabled, project
+from .projection import (GradLink, bias_fold_enabled, gate_bias_columns, gemm_backend, grad_link_enabled,
+                         project, will_run_native)
 
 
 def _load_scripted_ops() -> bool:
@@ -287,10 +288,11 @@ class SRUCell(nn.Module):
                                 scale_val: Optional[Tensor], mask_c: Optional[Tensor],
                                 mask_pad: Optional[Tensor]) -> List[Tensor]:
         link, self._grad_link = getattr(self, "_grad_link", None), None
+        folded, self._bias_folded = getattr(self, "_bias_folded", False), False
         return ops.elementwise_recurrence_gpu(U, residual, V, self.bias, c0, self.activation_type,
                                               self.hidden_size, self.bidirectional, self.has_skip_term,
                                               scale_val, mask_c, mask_pad, self.amp_recurrence_fp16,
-                                              grad_link=link)
+                                              grad_link=link, bias_in_u=folded)
 
     def compute_UV(self, input: Tensor, c0: Optional[Tensor],
                    mask_pad: Optional[Tensor]) -> Tuple[Tensor, Tensor]:
@@ -324,9 +326,18 @@ class SRUCell(nn.Module):
 
     @torch.jit.unused
     def _compute_U_eager(self, x: Tensor) -> Tensor:
+        """The projection on this package's GEMM.  When that GEMM is the tcgen05 kernel (16-bit compute type), the
+        gate bias is added to U in its epilogue and the recurrence is told so (it then runs without a bias and still
+        returns grad_bias); other products leave the bias to the recurrence, as the reference does."""
+        self._bias_folded = False
         if self.weight_proj is not None:
-            return project(project(x, self.weight_proj), self.weight)
-        return project(x, self.weight, link=getattr(self, "_grad_link", None))
+            x = project(x, self.weight_proj)
+        col_bias = None
+        if bias_fold_enabled() and will_run_native(x, self.weight):
+            col_bias = gate_bias_columns(self.bias, self.output_size, self.num_matrices)
+            self._bias_folded = True
+        link = getattr(self, "_grad_link", None) if self.weight_proj is None else None
+        return project(x, self.weight, col_bias=col_bias, link=link)
 
     def get_dropout_mask_(self, size: Tuple[int, int], p: float) -> Tensor:
         """Inverted-dropout mask shared over time (sru/modules.py:380-387)."""

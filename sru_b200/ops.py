@@ -198,7 +198,7 @@ class ElementwiseRecurrence(Function):
 
     @staticmethod
     def forward(ctx, u, x, weight_c, bias, init, activation_type, d_out, bidirectional,
-                has_skip_term, scale_x, mask_c=None, mask_pad=None, grad_link=None):
+                has_skip_term, scale_x, mask_c=None, mask_pad=None, grad_link=None, bias_in_u=False):
         length, batch, dirs, k, skip_type, is_custom = _geometry(u, x, d_out, bidirectional,
                                                                  has_skip_term, weight_c)
         st = u.dtype
@@ -207,7 +207,9 @@ class ElementwiseRecurrence(Function):
         u_c = u.detach().contiguous()
         x_c = x.detach().to(st).contiguous() if skip_type == 1 else None
         wc_c = weight_c.detach().to(st if is_custom else sm).contiguous()
-        bias_c = _prep_small(bias, sm)
+        # bias_in_u: the producer of U has already added the bias (GEMM epilogue); the kernels then take no bias,
+        # and the backward still delivers grad_bias (the sums it forms do not depend on where the bias was added)
+        bias_c = None if bias_in_u else _prep_small(bias, sm)
         init_c = _prep_small(init, sm)
         mask_c_c = _prep_small(mask_c, sm)
         pad_c = mask_pad.bool().contiguous() if mask_pad is not None else None
@@ -226,7 +228,7 @@ class ElementwiseRecurrence(Function):
                                  and x.dtype == st and x.is_contiguous()) else None
         if x.dim() == 2:
             h = h.squeeze(0)
-        return h, c_last.to(init.dtype) if init.dtype != c_last.dtype else c_last
+        return h, c_last
 
     @staticmethod
     def backward(ctx, grad_h, grad_last):
@@ -251,7 +253,7 @@ class ElementwiseRecurrence(Function):
                 grad_x = grad_x.view(x_shape).to(x_dtype)
         grad_wc = grad_wc.view(wc_shape).to(wc_dtype)
         return (grad_u, grad_x, grad_wc, grad_bias.to(bias_dtype), grad_init.view(init_shape).to(init_dtype),
-                None, None, None, None, None, None, None, None)
+                None, None, None, None, None, None, None, None, None)
 
 
 def elementwise_recurrence_forward(u: Tensor, x: Tensor, weight_c: Tensor, bias: Tensor, init: Tensor,
@@ -284,13 +286,14 @@ def elementwise_recurrence_gpu(U: Tensor, x: Tensor, weight_c: Tensor, bias: Ten
                                dropout_mask_c: Optional[Tensor] = None,
                                mask_pad: Optional[Tensor] = None,
                                amp_recurrence_fp16: bool = False,
-                               grad_link=None) -> List[Tensor]:
+                               grad_link=None, bias_in_u: bool = False) -> List[Tensor]:
     """Elementwise recurrence of SRU on the GPU; signature of sru/ops.py:98-110, plus ``grad_link``
-    (a projection.GradLink armed by the projection that produced U from the same x; optional).
+    (a projection.GradLink armed by the projection that produced U from the same x; optional) and
+    ``bias_in_u`` (U already contains the gate bias; ``bias`` is then only the tensor grad_bias belongs to).
 
     Returns ``[h, last_c]``.  In "reference" amp mode the casts of sru/ops.py:116-127 are
     applied first, so dtypes of the results equal the reference's; in "native" mode (default)
-    a 16-bit U is consumed as it is and h has U's dtype, last_c has c_init's dtype.
+    a 16-bit U is consumed as it is and h has U's dtype; last_c is float32 (see below).
     """
     _require_cuda(U, "U")
     if _amp_mode == "reference":
@@ -300,14 +303,19 @@ def elementwise_recurrence_gpu(U: Tensor, x: Tensor, weight_c: Tensor, bias: Ten
             cast = torch.Tensor.float
         U, x, c_init = cast(U), cast(x), cast(c_init)
         grad_link = None      # x is a cast copy here: its gradient is not the GEMM operand's
+    # The final state comes back as the reference's does (sru/ops.py:116-124 casts c_init before the scan): half
+    # precision with amp_recurrence_fp16 on a half U, float32 otherwise, whatever type c_init had.  A float32
+    # state also makes a sequence processed in chunks (state handed from chunk to chunk) bit-identical to one pass.
+    c_dtype = torch.float16 if (amp_recurrence_fp16 and U.dtype == torch.float16) else _small_dtype(U.dtype)
     if not torch.is_grad_enabled() or not any(
             t is not None and t.requires_grad for t in (U, x, weight_c, bias, c_init)):
-        h, c_last, _ = _forward_nograd(U, x, weight_c, bias, c_init, activation_type, hidden_size,
-                                       bidirectional, has_skip_term, scale_x, dropout_mask_c, mask_pad)
-        return [h, c_last.to(c_init.dtype)]
-    return list(ElementwiseRecurrence.apply(U, x, weight_c, bias, c_init, activation_type, hidden_size,
+        h, c_last, _ = _forward_nograd(U, x, weight_c, None if bias_in_u else bias, c_init, activation_type,
+                                       hidden_size, bidirectional, has_skip_term, scale_x, dropout_mask_c, mask_pad)
+        return [h, c_last.to(c_dtype)]
+    h, c_last = ElementwiseRecurrence.apply(U, x, weight_c, bias, c_init, activation_type, hidden_size,
                                             bidirectional, has_skip_term, scale_x, dropout_mask_c,
-                                            mask_pad, grad_link))
+                                            mask_pad, grad_link, bias_in_u)
+    return [h, c_last if c_last.dtype == c_dtype else c_last.to(c_dtype)]
 
 
 def _forward_nograd(U, x, weight_c, bias, c_init, activation_type, hidden_size, bidirectional,

@@ -33,12 +33,6 @@ def set_gemm_backend(name: str) -> None:
     _backend = name
 
 
-def _tma_compatible(x: Tensor, w: Tensor) -> bool:
-    """The tensor-map loads need 16-byte aligned bases and row pitches (multiples of 8 elements)."""
-    return (x.size(1) % 8 == 0 and w.size(1) % 8 == 0 and x.size(0) % 8 == 0
-            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
-
-
 def gemm(a: Tensor, b: Tensor, trans_a: bool = False, trans_b: bool = False,
          out_dtype: Optional[torch.dtype] = None, col_bias: Optional[Tensor] = None,
          out: Optional[Tensor] = None, accumulate: bool = False, name: Optional[str] = None) -> Tensor:
@@ -114,19 +108,30 @@ class GradLink:
 
 
 class _Projection(Function):
+    """x (M, K) in the 16-bit compute type times the MASTER weight w (K, N).  The weight is rounded to the compute
+    type inside (what autocast does in front of ``mm``), but its gradient leaves the weight-gradient GEMM in the
+    master's own type: with float32 parameters the fp32 accumulators are stored as they are, instead of being
+    rounded to 16 bits and cast back (one pass less, and no overflow of a half-precision sum over length * batch
+    rows under a loss scale)."""
+
     @staticmethod
     def forward(ctx, x, w, col_bias, link):
-        # x (M, K), w (K, N), both already in the 16-bit compute dtype
-        ctx.save_for_backward(x, w)
-        ctx.has_bias = col_bias is not None
+        dt = x.dtype
+        wc = w.detach()
+        if wc.dtype != dt:
+            wc = wc.to(dt)
+        if not wc.is_contiguous():
+            wc = wc.contiguous()
+        ctx.save_for_backward(x, wc)
+        ctx.w_dtype = w.dtype if w.dtype in (torch.float32,) + _SIXTEEN else dt
         ctx.link = link
-        return gemm(x, w, col_bias=col_bias)
+        return gemm(x, wc, col_bias=col_bias)
 
     @staticmethod
     def backward(ctx, grad_u):
         x, w = ctx.saved_tensors
         grad_u = grad_u.contiguous()
-        gx = gw = gb = None
+        gx = gw = None
         highway = None
         if ctx.link is not None:
             highway, ctx.link.grad_x = ctx.link.grad_x, None
@@ -140,34 +145,73 @@ class _Projection(Function):
                 if highway is not None:
                     gx = gx + highway.reshape(gx.shape).to(gx.dtype)
         if ctx.needs_input_grad[1]:
-            gw = gemm(x, grad_u, trans_a=True)            # (M,K)^T x (M,N) -> (K,N)
-        if ctx.has_bias and ctx.needs_input_grad[2]:
-            gb = grad_u.float().sum(0)
-        return gx, gw, gb, None
+            gw = gemm(x, grad_u, trans_a=True, out_dtype=ctx.w_dtype)     # (M,K)^T x (M,N) -> (K,N)
+        return gx, gw, None, None
 
 
-def project(x: Tensor, w: Tensor, col_bias: Optional[Tensor] = None,
-            link: Optional[GradLink] = None) -> Tensor:
-    """x (M, K) @ w (K, N) with autograd.  Follows autocast: inside an autocast region the
-    operands are cast to the autocast dtype, as ``Tensor.mm`` would be.  ``link`` (see GradLink)
-    is armed when x itself becomes the GEMM operand and x needs a gradient."""
-    if not x.is_cuda:
-        raise _lib.SruB200Error("sru_b200 has no CPU path: the projection input must be a CUDA tensor")
+_bias_fold_on = True
+
+
+def set_bias_fold_enabled(flag: bool) -> None:
+    """Gate bias added to U by the projection GEMM's epilogue (and the scan called without bias): on by default
+    for 16-bit projections on the tcgen05 kernel; off, the scan adds the bias itself."""
+    global _bias_fold_on
+    _bias_fold_on = bool(flag)
+
+
+def bias_fold_enabled() -> bool:
+    return _bias_fold_on
+
+
+def gate_bias_columns(bias: Tensor, width: int, k: int) -> Tensor:
+    """The layer's bias (2 * width,) laid out as float[width * k] for U's gate-innermost columns
+    (``sru_b200_gate_bias_columns``).  No gradient flows through it: grad_bias comes from the backward scan."""
+    b = bias.detach()
+    if b.dtype != torch.float32 or not b.is_contiguous():
+        b = b.float().contiguous()
+    out = torch.empty(width * k, dtype=torch.float32, device=b.device)
+    with torch.cuda.device(b.device):
+        _lib.call("gate_bias", 1, _lib.lib().sru_b200_gate_bias_columns, _lib.ptr(out), _lib.ptr(b), width, k,
+                  _lib.current_stream_ptr(b.device))
+    return out
+
+
+def _native_operand(x: Tensor, w: Tensor):
+    """The compute type of this product and x in that type, if the tcgen05 kernel takes it; else (None, None)."""
     dt = x.dtype
     if torch.is_autocast_enabled("cuda"):
         dt = torch.get_autocast_dtype("cuda")
     elif w.dtype != x.dtype:
         dt = w.dtype
-    if dt in _SIXTEEN and gemm_backend() == "tcgen05":
-        xc = x if x.dtype == dt else x.to(dt)
-        wc = w if w.dtype == dt else w.to(dt)
-        xc = xc if xc.is_contiguous() else xc.contiguous()
-        wc = wc if wc.is_contiguous() else wc.contiguous()
-        if _tma_compatible(xc, wc):
-            if link is not None:
-                link.armed = xc is x and x.requires_grad and torch.is_grad_enabled()
-            with torch.autocast("cuda", enabled=False):
-                return _Projection.apply(xc, wc, col_bias, link if link is not None and link.armed else None)
+    if dt not in _SIXTEEN or gemm_backend() != "tcgen05":
+        return dt, None
+    xc = x if x.dtype == dt else x.to(dt)
+    xc = xc if xc.is_contiguous() else xc.contiguous()
+    if not (xc.size(1) % 8 == 0 and w.size(1) % 8 == 0 and xc.size(0) % 8 == 0 and xc.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0 and w.is_contiguous()):
+        return dt, None      # the tensor-map loads need 16-byte aligned bases and row pitches
+    return dt, xc
+
+
+def will_run_native(x: Tensor, w: Tensor) -> bool:
+    """True if project(x, w) would run on the tcgen05 kernel (16-bit compute type, aligned shapes)."""
+    return x.is_cuda and _native_operand(x, w)[1] is not None
+
+
+def project(x: Tensor, w: Tensor, col_bias: Optional[Tensor] = None,
+            link: Optional[GradLink] = None) -> Tensor:
+    """x (M, K) @ w (K, N) (+ col_bias) with autograd.  Follows autocast: inside an autocast region the
+    operands are rounded to the autocast dtype, as ``Tensor.mm`` would.  ``link`` (see GradLink)
+    is armed when x itself becomes the GEMM operand and x needs a gradient.  ``col_bias`` is a constant here
+    (no gradient)."""
+    if not x.is_cuda:
+        raise _lib.SruB200Error("sru_b200 has no CPU path: the projection input must be a CUDA tensor")
+    dt, xc = _native_operand(x, w)
+    if xc is not None:
+        if link is not None:
+            link.armed = xc is x and x.requires_grad and torch.is_grad_enabled()
+        with torch.autocast("cuda", enabled=False):
+            return _Projection.apply(xc, w, col_bias, link if link is not None and link.armed else None)
     out = x.mm(w) if x.dtype == w.dtype or torch.is_autocast_enabled("cuda") else x.to(dt).mm(w)
     if col_bias is not None:
         out = out + col_bias.to(out.dtype)

@@ -162,3 +162,27 @@ def test_gemm_dynamic_tile_order(size, layout):
     _lib.check_device_error()
     assert torch.equal(dyn, static)
     assert rel_err(dyn32, _ref(a, b, ta, tb)) <= 1e-4
+
+
+def test_first_layer_products_full_size():
+    """The two products of benchmark configuration 5's first layer (120 -> 2048 per direction x 2, k = 4) at full
+    size: forward 256 000 x 8192 over K = 120 (two 64-wide k-blocks, the second partly out of range), and its weight
+    gradient 120 x 8192 over K = 256 000, which the library cuts into K slabs (fp32 partials + reduction kernel)."""
+    from conftest import check_parity
+    from sru_b200 import _lib
+    gemm = _gemm()
+    g = torch.Generator(device=DEV).manual_seed(17)
+    M, N, K = 256000, 8192, 120
+    a = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(K, N, device=DEV, generator=g) * 0.15).bfloat16()
+    out = gemm(a, w)
+    rows = torch.tensor([0, 63, 64, 128, 255, 256, 131071, 255999], device=DEV)
+    check_parity("gemm 256000x8192x120 fwd", "U rows", out[rows], a[rows].float() @ w.float(), 1e-2)
+    gu = (torch.randn(M, N, device=DEV, generator=g) * 0.1).bfloat16()
+    assert _lib.lib().sru_b200_gemm_workspace_bytes(K, N, M, 0) > 0      # a split is planned for this shape
+    gw = gemm(a, gu, trans_a=True, out_dtype=torch.float32)               # (M,120)^T x (M,8192)
+    cols = torch.arange(0, N, 257, device=DEV)
+    ref = a.float().t() @ gu[:, cols].float()
+    check_parity("gemm 120x8192x256000 wgrad", "grad_W cols", gw[:, cols], ref, 1e-3)
+    torch.cuda.synchronize()
+    _lib.check_device_error()

@@ -192,12 +192,11 @@ def test_dropout_mask_is_an_input():
         return m
 
     cpu = to_oracle(model).train()
-    it = iter(masks)
     for cell in model.rnn_lst:
         cell.get_dropout_mask_ = record.__get__(cell)
     h, c = model(x)
-    for cell in cpu.rnn_lst:
-        cell.get_dropout_mask_ = (lambda size, p, _it=it: next(_it))
+    it = iter(masks)
+    cpu.mask_source = lambda li, like, size, p: next(it)
     h_ref, c_ref = cpu(x.cpu())
     assert len(masks) == 2  # no dropout after the last layer
     assert rel_err(h, h_ref) <= 1e-5 and rel_err(c, c_ref) <= 1e-5
@@ -225,3 +224,112 @@ def test_sru_cuda_ops_backward_match_python_path():
         assert torch.equal(h, h2) and torch.equal(c, c2)
         assert torch.equal(gu, r[0]) and torch.equal(gx, r[1]) and torch.equal(gi, r[4])
         assert torch.equal(gwc.sum(1).view(-1), r[2]) and torch.equal(gb.sum(1).view(-1), r[3])
+
+
+def test_sru_cuda_general_backward_ops():
+    """sru_cuda::sru_backward / sru_bi_backward (the general operators: k = 4, tanh, custom per-step V) against the
+    ctypes path with the same arguments."""
+    from sru_b200 import _lib, ops
+    _lib.load_torch_ops()
+    g = torch.Generator().manual_seed(19)
+    L, B, d = 9, 4, 16
+    for bi, k, act, custom in ((False, 4, 0, False), (True, 4, 1, False), (False, 3, 1, True), (True, 4, 0, True)):
+        dirs = 2 if bi else 1
+        D = d * dirs
+        skip = 1 if k == 3 else 2
+        U = torch.randn(L, B, D * k, generator=g).to(DEV)
+        x = torch.randn(L, B, D, generator=g).to(DEV)
+        wc = (torch.randn(L, B, D * 2, generator=g) if custom else torch.randn(2 * D, generator=g)).to(DEV)
+        bias, c0 = torch.randn(2 * D, generator=g).to(DEV), torch.randn(B, D, generator=g).to(DEV)
+        mc = ((torch.rand(B, D, generator=g) > 0.2).float() / 0.8).to(DEV)
+        pad = (torch.rand(L, B, generator=g) > 0.7).to(DEV)
+        gh, gl = torch.randn(L, B, D, generator=g).to(DEV), torch.randn(B, D, generator=g).to(DEV)
+        fwd = torch.ops.sru_cuda.sru_bi_forward if bi else torch.ops.sru_cuda.sru_forward
+        bwd = torch.ops.sru_cuda.sru_bi_backward if bi else torch.ops.sru_cuda.sru_backward
+        xin = x if skip == 1 else None
+        h, c = fwd(U, xin, wc, bias, c0, mc, pad, L, B, d, k, act, skip, int(custom))
+        gu, gx, gwc, gb, gi = bwd(U, xin, wc, bias, c0, mc, pad, c, gh, gl, L, B, d, k, act, skip, int(custom))
+        h2, c2, _ = ops.scan_forward(U, xin, wc, bias, c0, mc, pad, L, B, d, dirs, k, act, skip, int(custom), 1.0)
+        r = ops.scan_backward(U, xin, wc, bias, c0, mc, pad, c2, gh, gl, L, B, d, dirs, k, act, skip, int(custom), 1.0)
+        assert _lib.last_scan_kernel() == ("generic" if (custom or act) else "pipelined")
+        assert torch.equal(h, h2) and torch.equal(c, c2)
+        assert torch.equal(gu, r[0]) and torch.equal(gi, r[4])
+        if skip == 1:
+            assert torch.equal(gx, r[1])
+        if custom:
+            assert torch.equal(gwc, r[2])
+        else:
+            assert torch.equal(gwc.sum(1).view(-1), r[2])
+        assert torch.equal(gb.sum(1).view(-1), r[3])
+
+
+@pytest.mark.parametrize("amp_dtype", [torch.bfloat16, torch.float16])
+def test_bias_in_gemm_epilogue_equals_bias_in_scan(amp_dtype):
+    """Gate bias added by the projection's epilogue (default for 16-bit projections) against the bias added inside the
+    scan: same outputs and gradients to 16-bit rounding, both within 2e-2 of the oracle; highway bias -3, k = 4 first
+    layer and k = 3 layers, low-rank chain."""
+    from sru_b200 import projection
+    for kw in (dict(input_size=64, hidden_size=128, num_layers=3, bidirectional=True, highway_bias=-3.0),
+               dict(input_size=128, hidden_size=128, num_layers=2, projection_size=32, highway_bias=-1.5, rescale=True)):
+        torch.manual_seed(21)
+        model = _sru()(**kw).to(DEV).train()
+        with torch.no_grad():
+            for cell in model.rnn_lst:
+                cell.bias.add_(torch.randn_like(cell.bias) * 0.5)
+        L, B = 33, 8
+        x = torch.randn(L, B, kw["input_size"], generator=torch.Generator().manual_seed(3)).to(DEV)
+        cpu = to_oracle(model, round_to=amp_dtype).train()
+        h_ref, _ = cpu(x.cpu().to(amp_dtype).float())
+        (h_ref ** 2).mean().backward()
+        ref = {n: p.grad for n, p in cpu.named_parameters()}
+        got = {}
+        for fold in (True, False):
+            projection.set_bias_fold_enabled(fold)
+            try:
+                model.zero_grad()
+                with torch.autocast("cuda", dtype=amp_dtype):
+                    h, _ = model(x)
+                    loss = (h.float() ** 2).mean()
+                loss.backward()
+            finally:
+                projection.set_bias_fold_enabled(True)
+            got[fold] = dict({n: p.grad.clone() for n, p in model.named_parameters()}, h=h.detach())
+            assert rel_err(h, h_ref) <= 2e-2
+        for n in got[True]:
+            assert rel_err(got[True][n], got[False][n]) <= 1e-2, (n, rel_err(got[True][n], got[False][n]))
+            if n != "h":
+                assert rel_err(got[True][n], ref[n]) <= 2e-2, (n, rel_err(got[True][n], ref[n]))
+
+
+def test_scale_x_changes_take_effect():
+    """The scalar the kernels take for scale_x is remembered between calls; every way the module itself changes the
+    buffer (reset_parameters, load_state_dict, versioned in-place ops) and forget_scale after a raw .data write
+    must reach the next forward."""
+    from sru_b200 import ops
+    torch.manual_seed(6)
+    model = _sru()(16, 16, num_layers=1, rescale=True).to(DEV).eval()
+    cell = model.rnn_lst[0]
+    x = torch.randn(5, 2, 16, device=DEV)
+    cpu = to_oracle(model).eval()
+
+    def agree():
+        with torch.no_grad():
+            h, _ = model(x)
+            cpu.rnn_lst[0].scale_x.copy_(cell.scale_x.cpu())
+            oh, _ = cpu(x.cpu())
+        return rel_err(h, oh) <= 1e-5
+
+    assert agree()
+    with torch.no_grad():
+        cell.scale_x.fill_(2.5)                     # versioned in-place write
+    assert agree()
+    cell.scale_x.data[0] = 0.75                     # the reference's own idiom: invisible to the version counter
+    ops.forget_scale(cell.scale_x)
+    assert agree()
+    sd = {k: v.clone() for k, v in model.state_dict().items()}
+    sd["rnn_lst.0.scale_x"] = torch.tensor([1.9])
+    model.load_state_dict(sd)
+    assert agree()
+    cell.reset_parameters()
+    cpu = to_oracle(model).eval()
+    assert agree()

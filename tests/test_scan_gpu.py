@@ -7,7 +7,7 @@ For 16-bit storage the oracle runs in fp32 on the same 16-bit-rounded inputs.
 import pytest
 import torch
 
-from conftest import rel_err
+from conftest import record_parity, rel_err
 from oracle import sru_oracle
 
 pytestmark = pytest.mark.gpu
@@ -25,8 +25,9 @@ def _opts(**kw):
     return _lib.options(**kw)
 
 
-def run_both(case_inputs, dtype, c_dtype=None, need_grad=True):
-    """Runs oracle (CPU) and CUDA on the same (dtype-rounded) inputs; returns two dicts."""
+def run_both(case_inputs, dtype, c_dtype=None, need_grad=True, expect_kernel=None):
+    """Runs oracle (CPU) and CUDA on the same (dtype-rounded) inputs; returns two dicts.
+    expect_kernel: (forward, backward) kernel family the library must report for these calls."""
     ops = _ops()
     (U, x, wc, bias, c0, mc, mp, gh, gl, L, B, d, dirs, k, act, skip, custom, scale) = case_inputs
     d_ = d
@@ -48,6 +49,10 @@ def run_both(case_inputs, dtype, c_dtype=None, need_grad=True):
                                          cu(c0.to(sm)), cu(None if mc is None else mc.to(sm)), pad,
                                          L, B, d, dirs, k, act, skip, int(custom), scale, True, c_dtype)
     out = dict(h=h, c_last=c_last, c_hist=c_hist)
+    from sru_b200 import _lib as _l
+    allowed = lambda e: (e,) if isinstance(e, str) else tuple(e)
+    if expect_kernel is not None:
+        assert _l.last_scan_kernel() in allowed(expect_kernel[0]), (_l.last_scan_kernel(), expect_kernel)
     if need_grad:
         # the oracle's backward consumes ITS c history; the kernel consumes its own
         ogu, ogx, ogwc, ogb, ogi = sru_oracle.backward(
@@ -60,6 +65,8 @@ def run_both(case_inputs, dtype, c_dtype=None, need_grad=True):
             cu(None if mc is None else mc.to(sm)), pad, c_hist, cu(ghs), cu(gl.to(sm)),
             L, B, d, dirs, k, act, skip, int(custom), scale)
         out.update(grad_u=gu, grad_x=gx, grad_wc=gwc, grad_bias=gb, grad_init=gi)
+        if expect_kernel is not None:
+            assert _l.last_scan_kernel() in allowed(expect_kernel[1]), (_l.last_scan_kernel(), expect_kernel)
     torch.cuda.synchronize()
     from sru_b200 import _lib
     _lib.check_device_error()
@@ -104,7 +111,16 @@ def run_both(case_inputs, dtype, c_dtype=None, need_grad=True):
     return out, ref
 
 
+FP32_CAP = 1e-4      # no conditioning argument widens the fp32 bar beyond this
+
+
 def compare(out, ref, tol, tag):
+    """Every tensor of `out` against `ref` at `tol`; the error reached goes into the session's parity report.
+
+    fp32 only: `ref` is then the fp64 oracle and carries, per tensor, how far the exact result moves under a
+    half-ulp perturbation of U and how far the fp32 CPU oracle itself lands from it ("drift").  A well-conditioned
+    case (4 x drift <= 1e-5) is held to the strict 1e-5; an ill-conditioned one to 4 x drift, never beyond FP32_CAP.
+    """
     drift = ref.get("_fp32_drift", {})
     for key, r in ref.items():
         if key == "_fp32_drift":
@@ -113,9 +129,12 @@ def compare(out, ref, tol, tag):
             assert out[key] is None, (tag, key)
             continue
         e = rel_err(out[key].reshape(r.shape), r)
-        # fp32: within 1e-5, or no further from the fp64 result than 4x the larger of the fp32 oracle's
-        # own drift and the problem's sensitivity to a half-ulp perturbation of U
-        assert e <= max(tol, 4.0 * drift.get(key, 0.0)), (tag, key, e, drift.get(key))
+        eff, note = tol, ""
+        if key in drift:
+            eff = min(max(tol, 4.0 * drift[key]), FP32_CAP)
+            note = "fp32; drift %.1e" % drift[key]
+        record_parity(tag, key, e, eff, note)
+        assert e <= eff, (tag, key, e, eff, drift.get(key))
 
 
 def golden_inputs(case, ):
@@ -156,7 +175,7 @@ def test_golden_cases(op_cases, dtype, force_generic):
     with _opts(force_generic=force_generic):
         for case in op_cases:
             inp = golden_inputs(case)
-            out, _ = run_both(inp, dtype)
+            out, _ = run_both(inp, dtype, expect_kernel=("generic", "generic") if force_generic else None)
             tol = TOL[dtype]
             gold = dict(h=case["h"], c_last=case["c_last"], grad_u=case["grad_U"], grad_x=case["grad_x"],
                         grad_wc=case["grad_weight_c"], grad_bias=case["grad_bias"],
@@ -184,11 +203,11 @@ def test_pipelined_vs_oracle(shape, dtype):
     L, B, d, dirs, k, pad = shape
     inp = random_inputs(L, B, d, dirs, k, pad=pad, scale=1.3, seed=L * 131 + B)
     for c_dtype in ([None] if dtype == torch.float32 else [torch.float32, dtype]):
-        out, ref = run_both(inp, dtype, c_dtype)
+        out, ref = run_both(inp, dtype, c_dtype, expect_kernel=(("pipelined", "split"), "pipelined"))
         compare(out, ref, TOL[dtype], (shape, dtype, c_dtype))
 
 
-@pytest.mark.parametrize("v", [1, 2, 4, 8])
+@pytest.mark.parametrize("v", [1, 2, 4])
 @pytest.mark.parametrize("threads", [32, 64, 128])
 @pytest.mark.parametrize("stages", [2, 5])
 def test_pipelined_tilings(v, threads, stages):
@@ -199,8 +218,8 @@ def test_pipelined_tilings(v, threads, stages):
             continue
         for (L, B, d, dirs, k, pad) in [(11, 5, 64, 2, 3, "tail"), (6, 3, 128, 1, 4, "random")]:
             inp = random_inputs(L, B, d, dirs, k, pad=pad, seed=v * 7 + threads)
-            with _opts(fwd_v=v, bwd_v=v, scan_threads=threads, scan_stages=stages):
-                out, ref = run_both(inp, dtype)
+            with _opts(fwd_v=v, bwd_v=v, scan_threads=threads, scan_stages=stages, fwd_split=0):
+                out, ref = run_both(inp, dtype, expect_kernel=("pipelined", "pipelined"))
             compare(out, ref, TOL[dtype], (v, threads, stages, dtype, L, B, d, dirs, k))
 
 
@@ -212,11 +231,11 @@ def test_pad_flags_across_stages(v, threads, ss):
     short of rows), both directions, random and tail padding."""
     for pad in ("random", "tail"):
         inp = random_inputs(71, 7, 64, 2, 3, pad=pad, seed=ss + v)
-        with _opts(fwd_v=v, bwd_v=v, scan_threads=threads, scan_stages=2, scan_ss=ss):
-            out, ref = run_both(inp, torch.bfloat16)
+        with _opts(fwd_v=v, bwd_v=v, scan_threads=threads, scan_stages=2, scan_ss=ss, fwd_split=0):
+            out, ref = run_both(inp, torch.bfloat16, expect_kernel=("pipelined", "pipelined"))
         compare(out, ref, TOL[torch.bfloat16], (v, threads, ss, pad))
-        with _opts(fwd_v=min(v, 2), bwd_v=v, scan_threads=threads, scan_stages=3, scan_ss=ss):
-            out, ref = run_both(inp, torch.float32)
+        with _opts(fwd_v=min(v, 2), bwd_v=v, scan_threads=threads, scan_stages=3, scan_ss=ss, fwd_split=0):
+            out, ref = run_both(inp, torch.float32, expect_kernel=("pipelined", "pipelined"))
         compare(out, ref, TOL[torch.float32], (v, threads, ss, pad, "fp32"))
 
 
@@ -322,3 +341,98 @@ def test_autograd_function_matches_oracle_autograd():
                 assert a.grad is None or float(a.grad.abs().max()) == 0.0
                 continue
             assert rel_err(a.grad, b.grad) <= 1e-5, (bi, k, name)
+
+
+def test_config2_first_layer_scan_at_size():
+    """The k = 4 first layer of benchmark configuration 2 at its full size (L=256, B=64, bidirectional 512 per
+    direction, bf16 storage, tail padding, unscaled N(0,1) inputs): every output and gradient against the oracle."""
+    inp = random_inputs(256, 64, 512, 2, 4, pad="tail", scale=1.0, seed=2024)
+    out, ref = run_both(inp, torch.bfloat16, expect_kernel=(("pipelined", "split"), "pipelined"))
+    compare(out, ref, TOL[torch.bfloat16], "config2 layer0 scan k=4")
+
+
+def _guarded(nbytes, dtype):
+    """A device tensor of nbytes / itemsize elements of `dtype` inside a buffer with 256-byte guard bands of 0xA5."""
+    raw = torch.full((nbytes + 512,), 0xA5, dtype=torch.uint8, device="cuda:0")
+    return raw, raw[256:256 + nbytes].view(dtype)
+
+
+def _bands_intact(raw, nbytes):
+    return bool((raw[:256] == 0xA5).all()) and bool((raw[256 + nbytes:] == 0xA5).all())
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shape", [
+    # L,  B, d, dirs, k     ragged everywhere: B not a multiple of the rows per tile, L not of the stage length
+    (13,  5, 8,  1, 3),    # hidden = one 16-byte granule of bf16 (two of fp32)
+    (37,  7, 64, 2, 3),
+    (9,   3, 16, 2, 4),
+    (131, 33, 128, 1, 3),
+])
+def test_no_write_outside_the_outputs(shape, dtype):
+    """Every output and the workspace sit between guard bands; after forward and backward through the C ABI the
+    bands are untouched and the results equal those of the ordinary call path (stand-in for a memory checker)."""
+    from sru_b200 import _lib
+    ops = _ops()
+    L, B, d, dirs, k = shape
+    D = d * dirs
+    inp = random_inputs(L, B, d, dirs, k, pad="tail", scale=1.2, seed=L + B)
+    (U, x, wc, bias, c0, mc, mp, gh, gl, *_r) = inp
+    dev = "cuda:0"
+    es = 2 if dtype == torch.bfloat16 else 4
+    Us, xs, ghs = U.to(dtype).to(dev), x.to(dtype).to(dev), gh.to(dtype).to(dev)
+    wcd, bd, c0d, mcd, gld = wc.to(dev), bias.to(dev), c0.to(dev), mc.to(dev), gl.to(dev)
+    pad = mp.to(dev).contiguous()
+    skip = 1 if k == 3 else 2
+    lib = _lib.lib()
+    code = _lib.DTYPE_CODE[dtype]
+    st = _lib.current_stream_ptr()
+    n = L * B * D
+    raw_h, h = _guarded(n * es, dtype)
+    raw_c, ch = _guarded(n * 4, torch.float32)
+    raw_l, cl = _guarded(B * D * 4, torch.float32)
+    rc = lib.sru_b200_scan_forward(h.data_ptr(), ch.data_ptr(), cl.data_ptr(), Us.data_ptr(),
+                                   xs.data_ptr() if skip == 1 else None, wcd.data_ptr(), bd.data_ptr(), c0d.data_ptr(),
+                                   mcd.data_ptr(), pad.data_ptr(), L, B, d, dirs, k, 0, skip, 0, 1.2, code, 0, st)
+    assert rc == 0, lib.sru_b200_last_error()
+    fwd_kernel = _lib.last_scan_kernel()
+    raw_gu, gu = _guarded(n * k * es, dtype)
+    raw_gx, gx = _guarded(n * es, dtype)
+    raw_gw, gwc = _guarded(2 * D * 4, torch.float32)
+    raw_gb, gb = _guarded(2 * D * 4, torch.float32)
+    raw_gi, gi = _guarded(B * D * 4, torch.float32)
+    wbytes = int(lib.sru_b200_scan_backward_workspace_bytes(L, B, d, dirs, k, code))
+    raw_ws, ws = _guarded(wbytes, torch.uint8)
+    rc = lib.sru_b200_scan_backward(gu.data_ptr(), gx.data_ptr() if skip == 1 else None, gwc.data_ptr(), gb.data_ptr(),
+                                    gi.data_ptr(), Us.data_ptr(), xs.data_ptr() if skip == 1 else None, wcd.data_ptr(),
+                                    bd.data_ptr(), c0d.data_ptr(), mcd.data_ptr(), pad.data_ptr(), ch.data_ptr(),
+                                    ghs.data_ptr(), gld.data_ptr(), L, B, d, dirs, k, 0, skip, 0, 1.2, code, 0,
+                                    ws.data_ptr(), wbytes, st)
+    assert rc == 0, lib.sru_b200_last_error()
+    torch.cuda.synchronize()
+    _lib.check_device_error()
+    assert fwd_kernel in ("pipelined", "split") and _lib.last_scan_kernel() == "pipelined"
+    for name, raw, nb in (("h", raw_h, n * es), ("c_hist", raw_c, n * 4), ("c_last", raw_l, B * D * 4),
+                          ("grad_u", raw_gu, n * k * es), ("grad_x", raw_gx, n * es), ("grad_wc", raw_gw, 2 * D * 4),
+                          ("grad_bias", raw_gb, 2 * D * 4), ("grad_init", raw_gi, B * D * 4), ("workspace", raw_ws, wbytes)):
+        assert _bands_intact(raw, nb), (name, shape, dtype)
+    # same results as the ordinary path (fresh allocations)
+    h2, ch2, cl2 = ops.scan_forward(Us, xs if skip == 1 else None, wcd, bd, c0d, mcd, pad, L, B, d, dirs, k, 0, skip,
+                                    0, 1.2, True, torch.float32)
+    r = ops.scan_backward(Us, xs if skip == 1 else None, wcd, bd, c0d, mcd, pad, ch2, ghs, gld, L, B, d, dirs, k, 0,
+                          skip, 0, 1.2)
+    assert torch.equal(h.view(L, B, D), h2) and torch.equal(ch.view(L, B, D), ch2) and torch.equal(cl.view(B, D), cl2)
+    assert torch.equal(gu.view(L, B, D * k), r[0]) and torch.equal(gi.view(B, D), r[4])
+    assert torch.equal(gwc, r[2]) and torch.equal(gb, r[3])
+    if skip == 1:
+        assert torch.equal(gx.view(L, B, D), r[1])
+
+
+def test_options_interface():
+    from sru_b200 import _lib
+    assert _lib.get_option("fwd_v") == -1
+    with _lib.options(fwd_v=2):
+        assert _lib.get_option("fwd_v") == 2
+    assert _lib.get_option("fwd_v") == -1
+    with pytest.raises(_lib.SruB200Error):
+        _lib.set_option("no_such_option", 1)

@@ -100,3 +100,20 @@ def test_noalloc_refuses_problems_beyond_its_scratch():
     assert rc == -3
     msg = L.sru_b200_last_error().decode()
     assert "scratch" in msg and str(limit) in msg
+    # one column beyond the limit is refused, again before any pointer is looked at
+    rc = fn(*([None] * 15), 4, 524289, 1, 1, 3, 0, 1, 0, 1.0, 0, 0, None)
+    assert rc == -3
+
+
+def test_noalloc_accepts_a_problem_exactly_at_its_limit():
+    """batch * dirs * hidden = 256 * 2 * 1024 = 524288 columns need exactly the 8 MiB the library holds."""
+    from sru_b200 import _lib
+    L, fn = _entry_points()
+    p = _problem(4, 256, 1024, 2, 3, torch.bfloat16, seed=4)
+    code = _lib.DTYPE_CODE[torch.bfloat16]
+    assert L.sru_b200_scan_backward_workspace_bytes(4, 256, 1024, 2, 3, code) == L.sru_b200_scan_backward_noalloc_max_bytes()
+    expected = _run(p, noalloc=False)
+    got = _run(p, noalloc=True)
+    for e, a in zip(expected, got):
+        assert torch.equal(e, a)
+    _lib.check_device_error()
