@@ -9,8 +9,12 @@ with inputs resident in HBM; `e2e` is the same step through the public module AP
 step's input copied from pinned host memory and the loss read back inside the timed region.
 `roofline` describes the kernel class that takes the most time (CUDA events around every
 C-ABI launch in a separate instrumented pass); `kernels` lists every class.  `cpu_baseline`
-(N = 1 only) times the CPU oracle model on a bounded sample of the same workload.
-`--impl reference` times that CPU implementation instead, with all host threads.
+(N = 1 only) times the CPU implementation on a bounded sample of the same workload (1 warm-up
++ 3 timed steps, median): for forward-only workloads the reference's own compiled CPU operator
+(kind "reference", when its library was built beside the oracle), else the C restatement of the
+reference's CPU path (kind "port").  `--impl reference` times that CPU implementation instead,
+with all host threads, and imports nothing of the shipped package.  `check` carries the loss and
+a float64 checksum of one layer's reduced weight gradient, equal at every N up to summation order.
 """
 import argparse
 import json
@@ -38,7 +42,8 @@ CONFIGS = {
     3: dict(name="config3: 6-layer uni SRU 2048, projection 512, highway_bias -3, fp16 autocast, L=512 B=32",
             L=512, B=32, amp=torch.float16,
             kwargs=dict(input_size=2048, hidden_size=2048, num_layers=6, projection_size=512,
-                        highway_bias=-3.0), x_std=0.5, lens=None, loss="meansq", train=True, c0=True),
+                        highway_bias=-3.0), x_std=0.5, lens=None, loss="meansq", train=True, c0=True,
+            loss_scale=65536.0),   # static loss scale, as a GradScaler would hold (fp16 gradients underflow without)
     4: dict(name="config4: 1-layer uni SRU 1024, bf16, L=8192 B=16, inference", L=8192, B=16, amp=None,
             kwargs=dict(input_size=1024, hidden_size=1024, num_layers=1), x_std=1.0, lens=None, loss=None,
             train=False, param_dtype=torch.bfloat16),
@@ -211,22 +216,57 @@ def run_step(model, cfg, x, mask, c0, tokens_global, reducer=None):
         loss = h.float().sum()
     else:
         loss = (h.float() ** 2).sum() / float(tokens_global * D)
-    loss.backward()
+    scale = cfg.get("loss_scale", 1.0)
+    (loss * scale if scale != 1.0 else loss).backward()
     if reducer is not None:
         reducer.finish()
     return loss.detach()
 
 
-def cpu_baseline(cfg, cfg_id, threads, sample_B, steps=1, warmup=0):
-    """Times the CPU oracle model (restatement of the reference's CPU path) on sample_B sequences."""
+def _reference_cpu_op():
+    """The reference's own compiled CPU scan (forward only), if its library was built beside the oracle."""
+    so = os.path.join(ROOT, "oracle", "_ref", "libsru_cpu_ref.so")
+    if not os.path.exists(so):
+        return None
+    try:
+        torch.ops.load_library(so)
+        return torch.ops.sru_cpu
+    except (OSError, RuntimeError):
+        return None
+
+
+def cpu_baseline(cfg, cfg_id, threads, sample_B, steps=3, warmup=1):
+    """Times the CPU implementation of the path on sample_B sequences.  Returns (tokens per step, step times, kind).
+
+    Training workloads: the oracle model (C restatement of the reference's CPU training path, whose own form is a
+    Python loop over time steps, sru/ops.py:205-248): kind "port".  Forward-only workloads: the same layer stack
+    with the recurrence done by the reference's own compiled operator sru_cpu::cpu_forward / cpu_bi_forward
+    (sru/csrc/sru_cpu_impl.cpp:56-226): kind "reference"; "port" if that library is absent.
+    Nothing of the shipped package is imported here.
+    """
     from oracle import sru_oracle
-    from oracle.cpu_model import to_oracle
-    from sru_b200.modules import SRU
+    from oracle.ref_model import OracleSRU
     torch.set_num_threads(threads)
     sru_oracle.set_threads(threads)
     torch.manual_seed(0)
-    model = to_oracle(SRU(**cfg["kwargs"]))
+    kw = dict(cfg["kwargs"])
+    model = OracleSRU(kw.pop("input_size"), kw.pop("hidden_size"), **kw)
     model.train(cfg["train"])
+    kind = "port"
+    if not cfg["train"]:
+        ops = _reference_cpu_op()
+        if ops is not None:
+            kind = "reference"
+
+            def recurrence(U, x, V, bias, c0, act, d, bi, skip, scale, mask_c, mask_pad):
+                L_, B_ = x.size(0), x.size(1)
+                k = U.size(-1) // d // (2 if bi else 1)
+                fn = ops.cpu_bi_forward if bi else ops.cpu_forward
+                h, c = fn(U.contiguous(), x.contiguous(), V.contiguous(), bias.contiguous(), c0.contiguous(),
+                          None if mask_pad is None else mask_pad.bool().contiguous(), L_, B_, d, k, act, skip,
+                          1.0 if scale is None else float(scale), False)
+                return h, c
+            model.recurrence = recurrence
     x, mask = make_inputs(cfg, cfg_id, sample_B)
     tokens = cfg["L"] * sample_B
     times = []
@@ -242,7 +282,17 @@ def cpu_baseline(cfg, cfg_id, threads, sample_B, steps=1, warmup=0):
                 model(x, mask_pad=mask)
         if i >= warmup:
             times.append(time.perf_counter() - t0)
-    return tokens, times
+    return tokens, times, kind
+
+
+def traffic_ratios():
+    """DRAM bytes / algorithmic bytes per kernel class, from the ncu captures summarised beside the profiles."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    try:
+        with open(path) as f:
+            return json.load(f)
+    except (OSError, ValueError):
+        return {}
 
 
 def main():
@@ -256,6 +306,17 @@ def main():
     ap.add_argument("--cuda-graph", action="store_true",
                     help="capture the step in one CUDA graph and time its replays (1 GPU; for launch-bound configs)")
     ap.add_argument("--cpu-sample-batch", type=int, default=0)
+    ap.add_argument("--reduce-dtype", default="fp32", choices=["fp32", "bf16"],
+                    help="N > 1: type the layer gradient buckets are all-reduced in")
+    ap.add_argument("--no-defer", action="store_true",
+                    help="N > 1: start a layer's all-reduce as soon as its bucket is complete instead of behind the "
+                         "next backward scan")
+    ap.add_argument("--nccl-max-ctas", type=int, default=0,
+                    help="N > 1: cap on the CTAs NCCL uses per collective (NCCL_MAX_CTAS), 0 = NCCL's default")
+    ap.add_argument("--no-bias-fold", action="store_true",
+                    help="leave the gate bias to the scan instead of the GEMM epilogue (A/B measurement)")
+    ap.add_argument("--sustain-seconds", type=float, default=3.0,
+                    help="N > 1: after the timed steps, keep stepping for about this long and report that step time too")
     ap.add_argument("--batch", type=int, default=0,
                     help="override the global batch (profiling on a small case; the workload name says so)")
     ap.add_argument("--length", type=int, default=0,
@@ -275,7 +336,7 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     metric = "sru_fwd_bwd_tokens_per_sec" if cfg["train"] else "sru_fwd_tokens_per_sec"
     host_cores = os.cpu_count() or 1
-    sample_B = args.cpu_sample_batch or {1: 32, 2: 4, 3: 1, 4: 1, 5: 1}[args.config]
+    sample_B = args.cpu_sample_batch or {1: 32, 2: 8, 3: 2, 4: 2, 5: 4}[args.config]
     sample_desc = "%s at batch %d of %d (all layers, full length, fp32 on CPU)" % (
         cfg["name"].split(":")[0], sample_B, cfg["B"])
 
@@ -283,8 +344,8 @@ def main():
         if rank != 0:
             return
         threads = host_cores
-        tokens, times = cpu_baseline(cfg, args.config, threads, sample_B, steps=max(1, args.steps),
-                                     warmup=min(args.warmup, 1))
+        tokens, times, kind = cpu_baseline(cfg, args.config, threads, sample_B, steps=max(1, args.steps),
+                                           warmup=min(args.warmup, 1))
         ms = 1e3 * sum(times) / len(times)
         val = tokens / (ms / 1e3)
         print(json.dumps({
@@ -292,7 +353,7 @@ def main():
             "steps": len(times), "warmup": min(args.warmup, 1), "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": cfg["name"], "sample": sample_desc},
-            "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port",
+            "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": kind,
                              "sample": sample_desc},
             "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         }))
@@ -303,9 +364,14 @@ def main():
     from sru_b200.distributed import LayerGradAllReducer, shard_batch
     from sru_b200.projection import gemm_backend
     _lib.lib()  # fail loudly here if the native library is missing
+    if args.no_bias_fold:
+        from sru_b200 import projection
+        projection.set_bias_fold_enabled(False)
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
+        if args.nccl_max_ctas > 0:
+            os.environ["NCCL_MAX_CTAS"] = str(args.nccl_max_ctas)     # this script is the launcher of its ranks
         dist.init_process_group("nccl", device_id=device)
     if world != args.gpus and rank == 0:
         sys.stderr.write("warning: --gpus %d but WORLD_SIZE %d\n" % (args.gpus, world))
@@ -326,7 +392,10 @@ def main():
     if cfg.get("c0"):
         dirs = 2 if cfg["kwargs"].get("bidirectional") else 1
         c0 = torch.zeros(cfg["kwargs"]["num_layers"], B_local, cfg["kwargs"]["hidden_size"] * dirs, device=device)
-    reducer = LayerGradAllReducer(model) if (cfg["train"] and world > 1) else None
+    reducer = None
+    if cfg["train"] and world > 1:
+        reducer = LayerGradAllReducer(model, reduce_dtype=torch.bfloat16 if args.reduce_dtype == "bf16" else None,
+                                      defer_to_scan_end=not args.no_defer)
 
     def barrier():
         if world > 1:
@@ -406,6 +475,31 @@ def main():
     ms_e2e = max_over_ranks(e0.elapsed_time(e1)) / args.steps
     h2d = x_pin.numel() * x_pin.element_size() + (0 if mask_pin is None else mask_pin.numel())
 
+    # ---- what the step computed: the loss and a checksum of one layer's (reduced) weight gradient ----
+    check = None
+    if cfg["train"]:
+        out_loss = run_step(model, cfg, x_dev, mask_dev, c0, tokens_global, reducer)
+        loss_t = out_loss.double().clone()
+        if world > 1:
+            dist.all_reduce(loss_t)          # each rank holds the loss of its shard, normalised by the global count
+        wlast = model.rnn_lst[-1].weight.grad.double() / cfg.get("loss_scale", 1.0)
+        check = {"loss": float(loss_t), "grad_weight_last_layer_sum": float(wlast.sum()),
+                 "grad_weight_last_layer_abs_sum": float(wlast.abs().sum())}
+
+    # ---- N > 1: the same step over a longer stretch (power-limited steady state), reported beside the timed steps ----
+    sustained = None
+    if world > 1 and args.sustain_seconds > 0:
+        n_more = max(args.steps, int(math.ceil(args.sustain_seconds * 1e3 / max(ms_per_step, 1e-3))))
+        barrier()
+        e0.record()
+        for _ in range(n_more):
+            step_resident()
+        e1.record()
+        barrier()
+        ms_more = max_over_ranks(e0.elapsed_time(e1)) / n_more
+        sustained = {"steps": n_more, "ms_per_step": ms_more, "value": tokens_global / (ms_more / 1e3),
+                     "unit": "tokens/s"}
+
     # ---- instrumented pass: CUDA events around every C-ABI launch ----
     _lib.timer = _lib.KernelTimer()
     for _ in range(2):
@@ -453,8 +547,9 @@ def main():
         top = max(cands, key=lambda k: cands[k]["ms_per_step"])
         t = cands[top]
         # DRAM traffic per launch: ratio of measured dram bytes to algorithmic bytes from the ncu captures
-        # summarised under profiles/ (small case of the same kernels), applied to this run's units.
-        ratio = {"scan_fwd": 0.93, "scan_fwd_infer": 0.93, "scan_bwd": 0.97, "gemm_all": 0.89}.get(top)
+        # (small case of the same kernels; the capture's summary writes the ratios to a file), applied to this
+        # run's units.
+        ratio = traffic_ratios().get(top, {}).get("dram_over_algorithmic")
         alg = {"scan_fwd": work["scan_fwd_bytes"], "scan_fwd_infer": work["scan_fwd_bytes"],
                "scan_bwd": work["scan_bwd_bytes"], "gemm_all": work["gemm_bytes"]}.get(top)
         if top == "gemm_all":
@@ -465,7 +560,7 @@ def main():
         traffic = (ratio * alg / max(1, n_launch)) if (ratio and alg) else None
         roofline = {"kernel": top, "bound": t["bound"], "achieved": t["achieved"], "peak": t["peak"],
                     "unit": t["unit"], "frac": t["frac"], "traffic": traffic,
-                    "traffic_note": "bytes per launch; ncu dram bytes / algorithmic bytes from profiles/, scaled by units",
+                    "traffic_note": "bytes per launch; ncu dram bytes / algorithmic bytes of a small case, scaled by units",
                     "peak_source": peaks["source"]}
 
     out = {
@@ -477,19 +572,26 @@ def main():
         "config": {"workload": cfg["name"], "global_batch": cfg["B"], "seq_len": cfg["L"],
                    "parallelism": "batch-sharded dp%d" % world, "l2": "inputs larger than L2",
                    "gemm": gemm_backend(), "c_hist": ops._c_hist_dtype, "amp_mode": ops.get_amp_mode(),
-                   "cuda_graph": graph is not None},
+                   "cuda_graph": graph is not None, "bias_in_gemm_epilogue": not args.no_bias_fold,
+                   "all_reduce": None if reducer is None else {
+                       "dtype": args.reduce_dtype, "bytes_per_step": reducer.bytes_per_step(),
+                       "start": "at bucket completion" if args.no_defer else "behind the next backward scan",
+                       "nccl_max_ctas": args.nccl_max_ctas or None}},
         "e2e": {"value": tokens_global / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": result_bytes},
         "gpu_launches": launches,
         "gpu_launches_per_step": launches // max(1, args.steps),
+        "check": check,
+        "sustained": sustained,
         "clocks": clocks,
         "roofline": roofline,
         "kernels": kernels,
     }
     if world == 1 and not args.no_cpu_baseline:
-        tokens, times = cpu_baseline(cfg, args.config, host_cores, sample_B, steps=1, warmup=0)
-        out["cpu_baseline"] = {"value": tokens / times[0], "unit": "tokens/s", "cores": host_cores, "kind": "port",
-                               "sample": sample_desc}
+        tokens, times, kind = cpu_baseline(cfg, args.config, host_cores, sample_B, steps=3, warmup=1)
+        med = sorted(times)[len(times) // 2]
+        out["cpu_baseline"] = {"value": tokens / med, "unit": "tokens/s", "cores": host_cores, "kind": kind,
+                               "sample": sample_desc + "; 1 warm-up + 3 timed steps, median"}
     print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()

@@ -152,6 +152,9 @@ class OracleSRU(nn.Module):
             layers.append(layer)
         self.rnn_lst = nn.ModuleList(layers)
         self.mask_source: Callable = _default_mask
+        # (U, x, V, bias, c0, activation_type, d, bidirectional, has_skip, scale_x, mask_c, mask_pad) -> (h, c_last);
+        # the benchmark's forward-only CPU baseline puts the reference's compiled operator here
+        self.recurrence: Callable = sru_oracle.elementwise_recurrence_oracle
 
     # ---- one layer: sru/modules.py:235-281 ----
     def _layer_forward(self, li: int, lay: _Layer, inp: torch.Tensor, c0: Optional[torch.Tensor],
@@ -185,7 +188,7 @@ class OracleSRU(nn.Module):
                 U, V = ret[0], ret[1] + lay.weight_c
             else:
                 U, V = ret, lay.weight_c
-        h, c = sru_oracle.elementwise_recurrence_oracle(
+        h, c = self.recurrence(
             U.to(real), skip_input.to(real), V.to(real), lay.bias.to(real), c0.to(real), lay.act, lay.d,
             lay.dirs == 2, lay.has_skip, None if scale is None else scale.to(real),
             None if mask_c is None else mask_c.to(real), mask_pad)

@@ -88,6 +88,34 @@ def build_torch_binding(force=False):
     return TORCH_SO
 
 
+TS_HOST = os.path.join(LIBDIR, "sru_b200_ts_host")
+
+
+def build_ts_host(force=False):
+    """The C++ host of tests/cpp/ts_host.cpp: a libtorch program linked against the operator binding the way a C++
+    application of the reference links libsru_cuda (sru/csrc/CMakeLists.txt:38-44: --no-as-needed, so that the
+    registrations run at load time).  Test infrastructure; returns the path of the executable."""
+    src = os.path.join(HERE, "..", "tests", "cpp", "ts_host.cpp")
+    if not os.path.exists(src):
+        return None
+    build_torch_binding()
+    if not force and not _stale(TS_HOST, [src, TORCH_SO]):
+        return TS_HOST
+    import torch
+    from torch.utils import cpp_extension as ce
+    incs = []
+    for p in ce.include_paths():
+        incs += ["-isystem", p]
+    tlib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cmd = ["g++", "-O1", "-std=c++17", "-w",
+           "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI)] + incs + [
+           src, "-o", TS_HOST, "-L" + LIBDIR, "-Wl,--no-as-needed", "-lsru_b200_torch", "-lsru_b200",
+           "-Wl,-rpath,$ORIGIN", "-L" + tlib, "-Wl,-rpath," + tlib, "-ltorch", "-ltorch_cpu", "-lc10", "-ltorch_cuda",
+           "-lc10_cuda", "-Wl,--as-needed", "-lpthread"]
+    subprocess.check_call(cmd)
+    return TS_HOST
+
+
 def build_all(force=False, verbose=False):
     return build_capi(force, verbose), build_torch_binding(force)
 

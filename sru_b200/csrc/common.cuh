@@ -25,7 +25,7 @@ int ensure_context();      // binds the device's primary context to this thread 
 enum Option {
     OPT_FWD_V, OPT_BWD_V, OPT_SCAN_THREADS, OPT_FWD_THREADS, OPT_BWD_THREADS, OPT_SCAN_SS, OPT_SCAN_STAGES,
     OPT_FORCE_GENERIC, OPT_FWD_SPLIT, OPT_GEMM_KSPLIT, OPT_GEMM_2SM, OPT_GEMM_EPI_WARPS, OPT_GEMM_DYNAMIC,
-    OPT_COUNT
+    OPT_GEMM_RASTER, OPT_COUNT
 };
 int option(Option o, int dflt);   // the option's value, or dflt when it is not set
 
@@ -102,14 +102,16 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                  : "memory");
 }
+// One probe of the barrier.  The thread is suspended by the hardware until the phase completes or about a
+// microsecond has passed (the hint), so a warp that waits costs its scheduler a probe per microsecond, not a spin.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(1000u)
         : "memory");
     return ok != 0;
 }

@@ -59,6 +59,7 @@ struct GemmArgs {
     int a_mn, b_mn;   // 1: MN-major operand
     uint32_t idesc;
     int tiles_m, tiles_n;
+    int raster_m;       // 1: consecutive tiles walk down M (column-major over the tile grid), 0: along N
     int ksplit, kbps;   // split-K: partial products over kbps k-blocks each go to slab sp of an fp32 workspace
     // Dynamic tile order (pair kernel): word 0 is the next-unit counter, then kSchedRing mailbox words per CTA pair.
     // NULL: static order (unit = pair, pair + pairs, ...).
@@ -146,13 +147,25 @@ struct GemmUnit {
     int tile, kb0, kb1;
     int sp;      // slab index of a split reduction (result row offset sp * M in the workspace)
 };
+// Units are numbered slab-major: all tiles of K slab 0, then all tiles of slab 1, ...  CTAs that run at the same
+// time then work on the same K range of neighbouring tiles and share their operand blocks through L2 (numbered
+// tile-major, concurrent units sit at different K offsets of one tile and nothing is shared: measured 20 % slower
+// on the 2048 x 6144 x 256 000 weight gradient, which became bound by HBM).
 __device__ __forceinline__ GemmUnit decode_unit(const GemmArgs &g, int unit, int nkb) {
     GemmUnit u;
-    u.tile = unit / g.ksplit;
-    u.sp = unit - u.tile * g.ksplit;
+    const int ntiles = g.tiles_m * g.tiles_n;
+    u.sp = unit / ntiles;
+    u.tile = unit - u.sp * ntiles;
     u.kb0 = u.sp * g.kbps;
     u.kb1 = min(nkb, u.kb0 + g.kbps);
     return u;
+}
+// Tile number -> block coordinates.  Which way consecutive tiles run decides what the concurrently running CTAs
+// share: along N they share a few row blocks of A and sweep all of B once per round of the persistent grid; along
+// M the other way round.  The host picks the direction that re-reads the SMALLER operand.
+__device__ __forceinline__ void tile_coords(const GemmArgs &g, int tile, int *mb, int *nb) {
+    if (g.raster_m) { *nb = tile / g.tiles_m; *mb = tile - *nb * g.tiles_m; }
+    else { *mb = tile / g.tiles_n; *nb = tile - *mb * g.tiles_n; }
 }
 
 // ---- PTX wrappers -----------------------------------------------------------------------
@@ -296,9 +309,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             uint32_t phase = 0;
             bool ok = true;
             for (int unit = blockIdx.x; unit < nunits && ok; unit += gridDim.x) {
-                const int tile = unit / g.ksplit, sp = unit - tile * g.ksplit;
-                const int kb0 = sp * g.kbps, kb1 = min(nkb, kb0 + g.kbps);
-                const int mb = tile / g.tiles_n, nb = tile % g.tiles_n;
+                const GemmUnit u = decode_unit(g, unit, nkb);
+                const int kb0 = u.kb0, kb1 = u.kb1;
+                int mb, nb;
+                tile_coords(g, u.tile, &mb, &nb);
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1)) { atomicExch(g.err, 11); ok = false; break; }
                     const uint32_t full = bar_full + 8 * stage;
@@ -335,8 +349,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const uint32_t a_step = g.a_mn ? 2048u : 32u, b_step = g.b_mn ? 2048u : 32u;
             const uint32_t a_lbo = g.a_mn ? 8192u : 16u, b_lbo = g.b_mn ? 8192u : 16u;
             for (int unit = blockIdx.x; unit < nunits && ok; unit += gridDim.x, ++it) {
-                const int tile = unit / g.ksplit, sp = unit - tile * g.ksplit;
-                const int kb0 = sp * g.kbps, kb1 = min(nkb, kb0 + g.kbps);
+                const GemmUnit u = decode_unit(g, unit, nkb);
+                const int kb0 = u.kb0, kb1 = u.kb1;
                 const int acc = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1;
                 if (!mbar_wait_bounded(bar_tempty + 8 * acc, acc_phase ^ 1)) { atomicExch(g.err, 12); break; }
@@ -364,9 +378,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int q = warp & 3;  // TMEM lane quarter this warp may address
         int it = 0;
         for (int unit = blockIdx.x; unit < nunits; unit += gridDim.x, ++it) {
-                const int tile = unit / g.ksplit, sp = unit - tile * g.ksplit;
-                const int kb0 = sp * g.kbps, kb1 = min(nkb, kb0 + g.kbps);
-            const int mb = tile / g.tiles_n, nb = tile % g.tiles_n;
+            const GemmUnit u = decode_unit(g, unit, nkb);
+            const int sp = u.sp;
+            int mb, nb;
+            tile_coords(g, u.tile, &mb, &nb);
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
             if (!mbar_wait_bounded(bar_tfull + 8 * acc, acc_phase)) { if (lane == 0) atomicExch(g.err, 14); break; }
@@ -494,6 +509,15 @@ __device__ __forceinline__ void epilogue_staged(const GemmArgs &g, uint32_t tmem
         for (int c = 0; c < 4; ++c) {
             const int64_t col0 = colh + c * 32;
             if (col0 >= g.N) break;
+            // the chunk's 32 bias values are requested BEFORE the accumulator load and its wait, so that their latency
+            // hides behind it (all lanes read the same addresses: one broadcast transaction per request)
+            float4 bv[8];
+            if (g.bias) {
+#pragma unroll
+                for (int q4 = 0; q4 < 8; ++q4)
+                    bv[q4] = (col0 + q4 * 4 < g.N) ? __ldg(reinterpret_cast<const float4 *>(g.bias + col0) + q4)
+                                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
             uint32_t r[32];
             tmem_ld32(tmem_warp + h * 128 + c * 32, r);
             tmem_ld_wait();
@@ -504,8 +528,7 @@ __device__ __forceinline__ void epilogue_staged(const GemmArgs &g, uint32_t tmem
                 for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[j0 + j]);
                 if (col0 + j0 < g.N) {
                     if (g.bias) {
-                        const float4 b0 = *reinterpret_cast<const float4 *>(g.bias + col0 + j0);
-                        const float4 b1 = *reinterpret_cast<const float4 *>(g.bias + col0 + j0 + 4);
+                        const float4 b0 = bv[j0 / 4], b1 = bv[j0 / 4 + 1];
                         v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
                         v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
                     }
@@ -602,7 +625,8 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 if (unit < 0) break;
                 const GemmUnit u = decode_unit(g, unit, nkb);
                 const int kb0 = u.kb0, kb1 = u.kb1;
-                const int mb = u.tile / g.tiles_n, nb = u.tile % g.tiles_n;
+                int mb, nb;
+                tile_coords(g, u.tile, &mb, &nb);
                 const int m0 = mb * 256 + (int)rank * 128;      // this CTA's rows of A
                 const int n0 = nb * BN + (int)rank * 128;       // this CTA's columns of B
                 for (int kb = kb0; kb < kb1; ++kb) {
@@ -690,7 +714,8 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             if (unit < 0) break;
             const GemmUnit u = decode_unit(g, unit, nkb);
             const int sp = u.sp;
-            const int mb = u.tile / g.tiles_n, nb = u.tile % g.tiles_n;
+            int mb, nb;
+            tile_coords(g, u.tile, &mb, &nb);
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
             if (!mbar_wait_bounded(bar_tfull + 8 * acc, acc_phase)) { if (lane == 0) atomicExch(g.err, 24); break; }
@@ -754,21 +779,37 @@ __global__ void splitk_reduce(const float *__restrict__ ws, int nsplit, int64_t 
     }
 }
 
-// How many K slabs to cut a product into: only when the tiles alone leave the last wave of the
-// persistent grid badly filled and the reduction is long enough to amortise the extra pass.
+// How many K slabs to cut a product into.  Two situations, both with a long reduction:
+//  * the tiles alone leave most of the persistent grid idle (2 * tiles <= workers: the first layer's weight
+//    gradient, 120 x 8192 over K = 256 000): slabs fill the grid, up to 3x faster;
+//  * the tiles make a few rounds of the grid with a badly filled last one (192 tiles on 74 pairs are 2.6 rounds of
+//    work done in 3: the 2048 x 6144 x 256 000 weight gradient): slabs make the rounds shorter and the last one
+//    fuller.  Units are numbered slab-major (decode_unit), which keeps the L2 sharing of the unsplit order.
+// Many rounds lose little to the last one and are left alone.
 int choose_ksplit(int64_t tiles, int workers, int nkb) {
     const int forced = option(OPT_GEMM_KSPLIT, 0);
     if (forced > 0) return std::min(forced, 16);
-    // Measured on B200: once the tiles fill at least half of the GPU, splitting only costs L2 reuse
-    // between concurrently running tiles; it pays (up to 3x) when the grid would be mostly idle.
-    if (nkb < 64 || 2 * tiles > (int64_t)workers) return 1;
-    int best = 1;
-    double best_eff = 0.0;
-    for (int s = 1; s <= 8; ++s) {
-        if (nkb / s < 16) break;
+    if (nkb < 64) return 1;
+    auto fill = [&](int s) {
         const int64_t units = tiles * s;
-        const double eff = (double)units / (double)(((units + workers - 1) / workers) * workers);
-        if (eff > best_eff + 0.04) { best_eff = eff; best = s; }
+        return (double)units / (double)(((units + workers - 1) / workers) * workers);
+    };
+    if (2 * tiles <= (int64_t)workers) {
+        int best = 1;
+        double best_eff = 0.0;
+        for (int s = 1; s <= 8; ++s) {
+            if (nkb / s < 16) break;
+            if (fill(s) > best_eff + 0.04) { best_eff = fill(s); best = s; }
+        }
+        return best;
+    }
+    if (tiles > 6 * (int64_t)workers || fill(1) >= 0.93) return 1;
+    int best = 1;
+    double best_eff = fill(1);
+    for (int s = 2; s <= 6; ++s) {
+        if (nkb / s < 64) break;
+        if (fill(s) >= 0.95) return s;                       // the smallest split that fills the rounds
+        if (fill(s) > best_eff + 0.04) { best_eff = fill(s); best = s; }
     }
     return best;
 }
@@ -916,6 +957,13 @@ static int gemm_impl(void *c, const void *a, const void *b, const float *col_bia
     g.ksplit = ksplit;
     g.kbps = kbps;
     const int64_t tiles_all = (int64_t)g.tiles_m * g.tiles_n;
+    // Tile order: with several rounds of tiles on the persistent grid, each round sweeps one operand completely and
+    // touches only a few blocks of the other; let the operand that is swept again and again be the smaller one
+    // (A is M x K, B is K x N: compare M with N).  The weight gradient x^T grad_U (2048 x 6144 over 256 000) reads
+    // 6 GB instead of 10 GB from HBM this way.  Option gemm_raster forces a direction.
+    g.raster_m = (tiles_all > plan.workers && m < n) ? 1 : 0;
+    const int raster_forced = option(OPT_GEMM_RASTER, -1);
+    if (raster_forced >= 0) g.raster_m = raster_forced ? 1 : 0;
     void *final_c = c;
     const int final_dtype = c_dtype, final_acc = g.accumulate;
     if (ksplit > 1) {   // partial products go to [ksplit][M][N] fp32; splitk_reduce finishes the job

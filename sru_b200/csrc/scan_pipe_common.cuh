@@ -12,6 +12,7 @@ namespace srub {
 constexpr int kTS = 4;            // time steps per pipeline stage
 constexpr int kBarBytes = 256;    // room for 2 * 16 mbarriers at the start of shared memory
 constexpr int kMaxStages = 16;
+constexpr int kSplitBarBytes = 768;  // split-role forward: full[16], empty[16], chain-ready[16][4]
 
 struct PipeArgs {
     ScanArgs a;
@@ -106,6 +107,9 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map
         : "memory");
 }
 
+// Split-role forward kernel (scan_split.cu): launched by launch_scan_pipelined with the maps and tile it prepared.
+int launch_scan_split(const ScanMaps &maps, const PipeArgs &p, cudaStream_t st);
+
 __host__ __device__ __forceinline__ uint32_t align128(uint32_t v) { return (v + 127u) & ~127u; }
 
 template <bool B> using BoolC = std::integral_constant<bool, B>;
@@ -144,6 +148,32 @@ template <typename P> __device__ __forceinline__ P lds_pack(uint32_t addr) {
         for (int i = 0; i < NB / 2; ++i) asm("ld.shared.u16 %0, [%1];" : "=h"(o[i]) : "r"(addr + 2 * i));
     }
     return out;
+}
+
+// Writes a Pack to global memory with an explicit global-space store: ld.shared and st.global cannot alias, so the
+// shared-memory loads of a later block may be scheduled above the stores of an earlier one (the split-role kernel's
+// follower warps, which work block by block, rely on it; measured on the one-role kernels it made no difference).
+template <typename P> __device__ __forceinline__ void stg_pack(void *gptr, const P &v) {
+    const size_t a = __cvta_generic_to_global(gptr);
+    constexpr int A = alignof(P), NB = sizeof(P);
+    if constexpr (A == 16) {
+        const uint4 *s = reinterpret_cast<const uint4 *>(&v);
+#pragma unroll
+        for (int i = 0; i < NB / 16; ++i)
+            asm volatile("st.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(a + 16 * i), "r"(s[i].x), "r"(s[i].y), "r"(s[i].z), "r"(s[i].w));
+    } else if constexpr (A == 8) {
+        const uint2 *s = reinterpret_cast<const uint2 *>(&v);
+#pragma unroll
+        for (int i = 0; i < NB / 8; ++i) asm volatile("st.global.v2.u32 [%0], {%1, %2};" ::"l"(a + 8 * i), "r"(s[i].x), "r"(s[i].y));
+    } else if constexpr (A == 4) {
+        const uint32_t *s = reinterpret_cast<const uint32_t *>(&v);
+#pragma unroll
+        for (int i = 0; i < NB / 4; ++i) asm volatile("st.global.u32 [%0], %1;" ::"l"(a + 4 * i), "r"(s[i]));
+    } else {
+        const uint16_t *s = reinterpret_cast<const uint16_t *>(&v);
+#pragma unroll
+        for (int i = 0; i < NB / 2; ++i) asm volatile("st.global.u16 [%0], %1;" ::"l"(a + 2 * i), "h"(s[i]));
+    }
 }
 
 // ---------------------------------------------------------------------------------------

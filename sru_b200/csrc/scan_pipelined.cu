@@ -154,18 +154,31 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const __grid_constant__ Sca
     const uint32_t x_off = u_region + r * x_slab + hc * sizeof(T);
     const uint32_t pad_off = u_region + x_region + r * SS;       // this row's flags of the stage
 
-    // One block of kTS steps.  ub / xb point at this thread's slice in the block's first time slab;
-    // dsu / dsx step to the next slab in scan order (negative for descending tiles).
-    auto block = [&](uint32_t ub, uint32_t xb, int dsu, int dsx, uint32_t pad_bits, int steps,
-                     auto pad_c, auto hist_c, auto full_c) {
+    // With two or more columns per thread the inputs of a step are requested one step ahead (software pipeline of
+    // depth one within a stage): up_n / xp_n hold the packs of the NEXT step while the current one is computed.
+    // Measured on B200 (one 2048-wide layer, L = 1000): V = 4 at batch 256 0.875 -> 0.948 of the HBM peak, V = 2 at
+    // batch 32 0.76 -> 0.84; one column per thread (16 K columns) lost 30 % with it, and so did the backward kernel
+    // (its four packs per step cost 40 registers and with them a resident CTA per SM), so those fetch at the step.
+    constexpr bool kAhead = (V >= 2);
+    Pack<T, V * K> up_n;
+    Pack<T, V> xp_n;
+    auto slab_of = [&](int j) { return asc ? j : SS - 1 - j; };   // j-th step of a stage in scan order
+    auto fetch = [&](uint32_t sb, int j) {
+        up_n = lds_pack<Pack<T, V * K>>(sb + u_off + slab_of(j) * su);
+        if (has_x) xp_n = lds_pack<Pack<T, V>>(sb + x_off + slab_of(j) * sx);
+    };
+
+    // One block of kTS steps starting q steps into the stage.
+    auto block = [&](uint32_t sb, int q, uint32_t pad_bits, int steps, auto pad_c, auto hist_c, auto full_c) {
         constexpr bool PAD = decltype(pad_c)::value, HIST = decltype(hist_c)::value, FULL = decltype(full_c)::value;
 #pragma unroll
         for (int ts = 0; ts < kTS; ++ts) {
             if (!FULL && ts >= steps) break;
             const bool pad = PAD && ((pad_bits >> (8 * ts)) & 0xffu);
-            const Pack<T, V * K> up = lds_pack<Pack<T, V * K>>(ub + ts * dsu);
-            Pack<T, V> xp;
-            if (has_x) xp = lds_pack<Pack<T, V>>(xb + ts * dsx);
+            if (!kAhead) fetch(sb, q + ts);
+            const Pack<T, V * K> up = up_n;
+            const Pack<T, V> xp = xp_n;
+            if (kAhead && q + ts + 1 < SS) fetch(sb, q + ts + 1);    // the slab exists in the stage even past the sequence end
             float hv[V];
 #pragma unroll
             for (int i = 0; i < V; ++i) {
@@ -204,16 +217,14 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const __grid_constant__ Sca
                 break;
             }
             const uint32_t sb = order_after_wait(smem_u32(stage0) + (uint32_t)s * stage_bytes);
+            if (kAhead && active) fetch(sb, 0);
             for (int q = 0; q < SS && n < L; q += kTS, n += kTS) {
                 if (active) {
-                    const int slab = asc ? q : (SS - 1 - q);
                     // the block's four flags, byte ts = scan step ts of the block
                     const uint32_t pad_cur = PADF ? pad_word(sb + pad_off, q, SS, asc) : 0u;
-                    const uint32_t ub = sb + u_off + slab * su;
-                    const uint32_t xb = sb + x_off + slab * sx;
                     const int64_t left = L - n;
-                    if (left >= kTS) block(ub, xb, asc ? su : -su, asc ? sx : -sx, pad_cur, kTS, pad_c, hist_c, BoolC<true>{});
-                    else block(ub, xb, asc ? su : -su, asc ? sx : -sx, pad_cur, (int)left, pad_c, hist_c, BoolC<false>{});
+                    if (left >= kTS) block(sb, q, pad_cur, kTS, pad_c, hist_c, BoolC<true>{});
+                    else block(sb, q, pad_cur, (int)left, pad_c, hist_c, BoolC<false>{});
                 }
             }
             __syncwarp();
@@ -362,21 +373,33 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const __grid_constant__ Sca
         const uint32_t g_off = u_region + x_region + c_region + r * g_slab + hc * sizeof(T);
         const uint32_t pad_off = in_region + r * SS;                 // this row's flags of the stage
 
-        // One block of kTS steps.  LAST marks the final block (ragged, and holding the step whose
-        // predecessor state is c_init); all other blocks are full and branch-free.
-        auto block = [&](uint32_t sb, int slab, int dslab, uint32_t pad_bits, int steps, auto pad_c, auto last_c) {
+        // The step's packs (fetched at the step: see the forward kernel for why not one step ahead).
+        Pack<T, V * K> up_n;
+        Pack<T, V> gh_n, xp_n;
+        Pack<TC, V> cp_n;
+        auto slab_of = [&](int j) { return asc ? j : SS - 1 - j; };
+        auto fetch = [&](uint32_t sb, int j) {
+            const int sl = slab_of(j);
+            up_n = lds_pack<Pack<T, V * K>>(sb + u_off + sl * su);
+            gh_n = lds_pack<Pack<T, V>>(sb + g_off + sl * sg);
+            if (has_x) xp_n = lds_pack<Pack<T, V>>(sb + x_off + sl * sx);
+            cp_n = lds_pack<Pack<TC, V>>(sb + c_off + sl * sc);
+        };
+
+        // One block of kTS steps starting q steps into the stage.  LAST marks the final block (ragged, and holding
+        // the step whose predecessor state is c_init); all other blocks are full and branch-free.
+        auto block = [&](uint32_t sb, int q, uint32_t pad_bits, int steps, auto pad_c, auto last_c) {
             constexpr bool PAD = decltype(pad_c)::value, LAST = decltype(last_c)::value;
 #pragma unroll
             for (int ts = 0; ts < kTS; ++ts) {
                 if (LAST && ts >= steps) break;
                 const bool pad = PAD && ((pad_bits >> (8 * ts)) & 0xffu);
                 const bool at_start = LAST && (ts == steps - 1);
-                const int sl = slab + ts * dslab;
-                const Pack<T, V * K> up = lds_pack<Pack<T, V * K>>(sb + u_off + sl * su);
-                const Pack<T, V> ghp = lds_pack<Pack<T, V>>(sb + g_off + sl * sg);
-                Pack<T, V> xp;
-                if (has_x) xp = lds_pack<Pack<T, V>>(sb + x_off + sl * sx);
-                const Pack<TC, V> cpp = lds_pack<Pack<TC, V>>(sb + c_off + sl * sc);
+                fetch(sb, q + ts);
+                const Pack<T, V * K> up = up_n;
+                const Pack<T, V> ghp = gh_n;
+                const Pack<T, V> xp = xp_n;
+                const Pack<TC, V> cpp = cp_n;
                 float guv[V * K], gxv_[V];
 #pragma unroll
                 for (int i = 0; i < V; ++i) {
@@ -442,11 +465,10 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const __grid_constant__ Sca
                 const uint32_t sb = order_after_wait(smem_u32(stage0) + (uint32_t)s * stage_bytes);
                 for (int q = 0; q < SS && m < L; q += kTS, m += kTS) {
                     if (active) {
-                        const int slab = asc ? q : (SS - 1 - q);
                         const uint32_t pad_cur = PADF ? pad_word(sb + pad_off, q, SS, asc) : 0u;
                         const int64_t left = L - m;   // steps left including this block
-                        if (left > kTS) block(sb, slab, asc ? 1 : -1, pad_cur, kTS, pad_c, BoolC<false>{});
-                        else block(sb, slab, asc ? 1 : -1, pad_cur, (int)left, pad_c, BoolC<true>{});
+                        if (left > kTS) block(sb, q, pad_cur, kTS, pad_c, BoolC<false>{});
+                        else block(sb, q, pad_cur, (int)left, pad_c, BoolC<true>{});
                     }
                 }
                 __syncwarp();
@@ -533,8 +555,10 @@ static int make_scan_map(CUtensorMap *map, const void *base, int64_t row_bytes, 
 }
 
 // Chooses V, the tile and the ring.  Returns false when the shape is not eligible.
+// split: geometry for the split-role forward kernel (scan_split.cu): at most two columns per thread, a second
+// set of consumer warps, and a float per column-step of shared memory in every stage for the states.
 static bool choose_tile(int64_t L, int64_t B, int64_t d, int dirs, int k, int skip_type, int dtype,
-                        int c_dtype, bool backward, bool has_pad, TileCfg *out) {
+                        int c_dtype, bool backward, bool has_pad, bool split, TileCfg *out) {
     const int s = (int)dtype_size(dtype);
     if (dtype == SRU_F64 || s == 0) return false;
     const int granule = 16 / s;  // elements per 16 bytes
@@ -570,8 +594,9 @@ static bool choose_tile(int64_t L, int64_t B, int64_t d, int dirs, int k, int sk
         else { v = 2; ntc = 128; }
     }
     while (ntc > 32 && ncols / ((int64_t)v * ntc) < (int64_t)sms / 2) ntc /= 2;   // tiny problems: spread over the SMs
+    if (split) v = std::min(v, 2);
     v = option(backward ? OPT_BWD_V : OPT_FWD_V, v);
-    if (v < vmin || v > vmax || (v & (v - 1))) return false;
+    if (v < vmin || v > (split ? 2 : vmax) || (v & (v - 1))) return false;
     ntc = option(OPT_SCAN_THREADS, ntc);
     ntc = option(backward ? OPT_BWD_THREADS : OPT_FWD_THREADS, ntc);
     if (ntc < 32 || ntc > 128 || ntc % 32) return false;
@@ -591,10 +616,13 @@ static bool choose_tile(int64_t L, int64_t B, int64_t d, int dirs, int k, int sk
     const int sc = (int)dtype_size(c_dtype);
     size_t per_row_step = (size_t)hw * (k * s + (has_x ? s : 0));
     if (backward) per_row_step += (size_t)hw * (sc + s);
+    if (split) per_row_step += (size_t)hw * sizeof(float);
+    const int cta_threads = (split ? 2 : 1) * cthreads + 32;
+    const size_t bar_bytes = split ? kSplitBarBytes : kBarBytes;
     // time steps per stage: one request should carry about 16 KB (fewer barrier round trips per
     // step), as long as three stages still fit the CTA's share of shared memory
     const int64_t nctas0 = ((B + br - 1) / br) * (D / hw);
-    const int cps0 = (int)std::min<int64_t>(std::max<int64_t>(1, (nctas0 + sms - 1) / sms), 2048 / (cthreads + 32));
+    const int cps0 = (int)std::min<int64_t>(std::max<int64_t>(1, (nctas0 + sms - 1) / sms), 2048 / cta_threads);
     const size_t ring0 = std::min<size_t>(200 * 1024 / cps0, 96 * 1024);
     int ss = kTS;
     while (ss < 32 && (size_t)ss * br * per_row_step < 16 * 1024 && (size_t)(2 * ss) * br * per_row_step * 3 <= ring0) ss *= 2;
@@ -604,29 +632,32 @@ static bool choose_tile(int64_t L, int64_t B, int64_t d, int dirs, int k, int sk
     auto stage_size = [&](int steps) {
         size_t t = align128((uint32_t)(steps * br * hw * k * s)) + align128((uint32_t)(has_x ? steps * br * hw * s : 0));
         if (backward) t += align128((uint32_t)(steps * br * hw * sc)) + align128((uint32_t)(steps * br * hw * s));
+        if (split) t += align128((uint32_t)(steps * br * hw * sizeof(float)));
         if (has_pad) t += align128((uint32_t)(steps * br));
         return t;
     };
+    // forced or derived, a stage length that leaves no room for two stages is shortened rather than refused
+    while (ss > kTS && bar_bytes + 2 * stage_size(ss) > 227 * 1024) ss -= kTS;
     const size_t stage_bytes = stage_size(ss);
     // ring: shared by the CTAs expected on one SM
     const int64_t nctas = ((B + br - 1) / br) * (D / hw);
-    int cta_per_sm = (int)std::min<int64_t>(std::max<int64_t>(1, (nctas + sms - 1) / sms), 2048 / (cthreads + 32));
+    int cta_per_sm = (int)std::min<int64_t>(std::max<int64_t>(1, (nctas + sms - 1) / sms), 2048 / cta_threads);
     size_t ring = std::min<size_t>(200 * 1024 / cta_per_sm, 96 * 1024);
     int ns = (int)(ring / stage_bytes);
     ns = std::max(2, std::min(ns, kMaxStages));
     ns = option(OPT_SCAN_STAGES, ns);
     ns = std::max(2, std::min(ns, kMaxStages));
-    size_t smem = kBarBytes + (size_t)ns * stage_bytes;
-    if (backward) smem = std::max(smem, kBarBytes + (size_t)br * 4 * hw * sizeof(float));
+    size_t smem = bar_bytes + (size_t)ns * stage_bytes;
+    if (backward) smem = std::max(smem, bar_bytes + (size_t)br * 4 * hw * sizeof(float));
     if (smem > 227 * 1024) {
-        ns = (int)((227 * 1024 - kBarBytes) / stage_bytes);
+        ns = (int)((227 * 1024 - bar_bytes) / stage_bytes);
         if (ns < 2) return false;
-        smem = kBarBytes + (size_t)ns * stage_bytes;
+        smem = bar_bytes + (size_t)ns * stage_bytes;
     }
     out->hw = hw; out->br = br; out->tpr = tpr;
     out->nht = (int)(D / hw); out->nrt = (int)((B + br - 1) / br);
     out->nstages = ns; out->ss = ss; out->v = v;
-    out->threads = cthreads + 32; out->smem = smem;
+    out->threads = cta_threads; out->smem = smem;
     return nctas <= 0x7fffffff;
 }
 
@@ -693,7 +724,20 @@ int launch_scan_pipelined(const ScanArgs &a, bool backward, cudaStream_t st) {
     if (!err) return set_error(SRU_ERR_CUDA, "device error flag unavailable");
     PipeArgs p;
     p.a = a;
-    if (!choose_tile(a.L, a.B, a.d, a.dirs, a.k, a.skip_type, a.dtype, a.c_dtype, backward, a.mask_pad != nullptr, &p.c)) return 0;
+    // Forward problems with few column-warps per SM go to the split-role kernel (option fwd_split: 1 always where
+    // the shape allows, 0 never).
+    bool split = false;
+    if (!backward) {
+        const int forced = option(OPT_FWD_SPLIT, -1);
+        const int64_t w = a.B * (int64_t)a.d * a.dirs / (32 * (int64_t)num_sms());
+        split = forced < 0 ? (w < 10) : (forced != 0);
+        if (split && !choose_tile(a.L, a.B, a.d, a.dirs, a.k, a.skip_type, a.dtype, a.c_dtype, false,
+                                  a.mask_pad != nullptr, true, &p.c))
+            split = false;
+    }
+    if (!split && !choose_tile(a.L, a.B, a.d, a.dirs, a.k, a.skip_type, a.dtype, a.c_dtype, backward,
+                               a.mask_pad != nullptr, false, &p.c))
+        return 0;
     p.err = err;
 
     // the tensor-map encoder is a driver entry point: this thread needs the primary context
@@ -715,6 +759,12 @@ int launch_scan_pipelined(const ScanArgs &a, bool backward, cudaStream_t st) {
         if (rc) return rc;
     }
 
+    if (split) {
+        rc = launch_scan_split(maps, p, st);
+        if (rc < 0) return rc;
+        note_scan_kernel(SCAN_KERNEL_SPLIT);
+        return 1;
+    }
     const int dt = a.dtype, ct = a.c_dtype;
     if (dt == SRU_F32 && ct == SRU_F32) rc = launch_k<float, float>(maps, p, backward, st);
     else if (dt == SRU_F16 && ct == SRU_F16) rc = launch_k<__half, __half>(maps, p, backward, st);

@@ -13,6 +13,7 @@
 #include <torch/library.h>
 #include <torch/types.h>
 
+#include <algorithm>
 #include <vector>
 
 #include "../../include/sru_b200.h"
@@ -168,7 +169,78 @@ std::vector<Tensor> sru_bi_backward(const Tensor &U, const OptTensor &x, const T
                          hidden_size, 2, k, activation_type, skip_type, is_custom);
 }
 
+// ---- operators of this package's own namespace: what the scripted module calls instead of library kernels ----
+
+// y = x (M, K) @ w (K, N) [+ col_bias] on the tcgen05 GEMM for 16-bit CUDA operands whose shapes the tensor-map
+// loads take (K, N multiples of 8, 16-byte aligned rows); anything else is the library product, like Tensor.mm.
+Tensor b200_gemm(const Tensor &x, const Tensor &w, const OptTensor &col_bias) {
+    TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && x.size(1) == w.size(0), "sru_b200::gemm: shapes (M,K) x (K,N) expected");
+    const auto st = x.scalar_type();
+    const bool sixteen = (st == at::kHalf || st == at::kBFloat16) && w.scalar_type() == st;
+    const int64_t m = x.size(0), k = x.size(1), n = w.size(1);
+    if (!(x.is_cuda() && sixteen && k % 8 == 0 && n % 8 == 0 && m > 0 && k > 0)) {
+        Tensor out = at::mm(x, w);
+        if (col_bias.has_value()) out = out + col_bias.value().to(out.scalar_type());
+        return out;
+    }
+    c10::cuda::CUDAGuard guard(x.device());
+    Tensor xc = x.contiguous(), wc = w.contiguous();
+    Tensor bias;
+    if (col_bias.has_value()) bias = col_bias.value().to(at::kFloat).contiguous();
+    Tensor out = at::empty({m, n}, x.options());
+    const int code = dtype_code(st);
+    const size_t wbytes = sru_b200_gemm_workspace_bytes(m, n, k, bias.defined() ? 1 : 0);
+    Tensor ws = at::empty({(int64_t)std::max<size_t>(wbytes, 16)}, x.options().dtype(at::kByte));
+    const int rc = sru_b200_gemm_ws(out.data_ptr(), xc.data_ptr(), wc.data_ptr(),
+                                    bias.defined() ? bias.data_ptr<float>() : nullptr, m, n, k, k, n, n, 0, 0, code,
+                                    code, 0, ws.data_ptr(), wbytes, at::cuda::getCurrentCUDAStream().stream());
+    TORCH_CHECK(rc == 0, "sru_b200::gemm failed: ", sru_b200_last_error());
+    return out;
+}
+
+// The layer's gate bias (2 * width) as the col_bias vector of U's gate-innermost columns.
+Tensor b200_gate_bias_columns(const Tensor &bias, int64_t width, int64_t k) {
+    TORCH_CHECK(bias.is_cuda() && bias.numel() == 2 * width, "sru_b200::gate_bias_columns: CUDA bias of 2*width expected");
+    c10::cuda::CUDAGuard guard(bias.device());
+    Tensor b = bias.to(at::kFloat).contiguous();
+    Tensor out = at::empty({width * k}, b.options());
+    const int rc = sru_b200_gate_bias_columns(out.data_ptr<float>(), b.data_ptr<float>(), width, (int)k,
+                                              at::cuda::getCurrentCUDAStream().stream());
+    TORCH_CHECK(rc == 0, "sru_b200::gate_bias_columns failed: ", sru_b200_last_error());
+    return out;
+}
+
+// Layer normalisation over the last dimension, forward only (the scripted module is an inference path); row lengths
+// the kernels do not take go to the library operator.
+Tensor b200_layer_norm(const Tensor &x, const OptTensor &weight, const OptTensor &bias, double eps) {
+    const int64_t n = x.size(-1);
+    const auto st = x.scalar_type();
+    const bool f32 = st == at::kFloat, sixteen = (st == at::kHalf || st == at::kBFloat16);
+    if (!(x.is_cuda() && (f32 || sixteen) && n > 0 && n <= 4096 && n % (f32 ? 4 : 8) == 0 && x.numel() > 0)) {
+        return at::layer_norm(x, {n}, weight, bias, eps);
+    }
+    c10::cuda::CUDAGuard guard(x.device());
+    Tensor xc = x.contiguous();
+    Tensor w, b;
+    if (weight.has_value()) w = weight.value().to(at::kFloat).contiguous();
+    if (bias.has_value()) b = bias.value().to(at::kFloat).contiguous();
+    Tensor y = at::empty_like(xc);
+    const int code = dtype_code(st);
+    const int rc = sru_b200_layer_norm_forward(y.data_ptr(), nullptr, nullptr, xc.data_ptr(),
+                                               w.defined() ? w.data_ptr<float>() : nullptr,
+                                               b.defined() ? b.data_ptr<float>() : nullptr, xc.numel() / n, n, eps, code,
+                                               code, at::cuda::getCurrentCUDAStream().stream());
+    TORCH_CHECK(rc == 0, "sru_b200::layer_norm failed: ", sru_b200_last_error());
+    return y;
+}
+
 }  // namespace
+
+TORCH_LIBRARY(sru_b200, m) {
+    m.def("gemm(Tensor x, Tensor w, Tensor? col_bias) -> Tensor", &b200_gemm);
+    m.def("gate_bias_columns(Tensor bias, int width, int k) -> Tensor", &b200_gate_bias_columns);
+    m.def("layer_norm(Tensor x, Tensor? weight, Tensor? bias, float eps) -> Tensor", &b200_layer_norm);
+}
 
 TORCH_LIBRARY(sru_cuda, m) {
     m.def("sru_forward_simple", &sru_forward_simple);

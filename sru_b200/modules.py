@@ -210,7 +210,24 @@ class SRUCell(nn.Module):
 
     def forward(self, input: Tensor, c0: Optional[Tensor] = None,
                 mask_pad: Optional[Tensor] = None) -> Tuple[Tensor, Tensor]:
-        """(length, batch, input_size) or (batch, input_size) -> (h, c_last), as sru/modules.py:235-281."""
+        """(length, batch, input_size) or (batch, input_size) -> (h, c_last), as sru/modules.py:235-281.
+        A layer called on its own hands back the types the reference would (float32 h for float32 input under
+        16-bit autocast); inside an ``SRU`` stack the layers pass the 16-bit h on (``forward_native``)."""
+        h, c = self.forward_native(input, c0, mask_pad)
+        if not torch.jit.is_scripting():
+            h = self._restore_output_dtype(h, input)
+        return h, c
+
+    @torch.jit.unused
+    def _restore_output_dtype(self, h: Tensor, input: Tensor) -> Tensor:
+        if ops.get_amp_mode() == "native" and h.dtype in (torch.float16, torch.bfloat16) \
+                and input.dtype == torch.float32 and not self.amp_recurrence_fp16:
+            return h.float()
+        return h
+
+    def forward_native(self, input: Tensor, c0: Optional[Tensor] = None,
+                       mask_pad: Optional[Tensor] = None) -> Tuple[Tensor, Tensor]:
+        """The layer, with h left in the type the recurrence wrote it in."""
         if input.dim() != 2 and input.dim() != 3:
             raise ValueError("Input must be 2 or 3 dimensional")
         batch_size = input.size(-2)
@@ -222,7 +239,7 @@ class SRUCell(nn.Module):
             if not torch.jit.is_scripting():
                 input = self._layer_norm_eager(input, True)
             else:
-                input = self.layer_norm(input)
+                input = self._layer_norm_scripted(input)
         if self.training and (self.rnn_dropout > 0):
             mask = self.get_dropout_mask_((batch_size, input.size(-1)), self.rnn_dropout)
             input = input * mask.expand_as(input)
@@ -241,8 +258,14 @@ class SRUCell(nn.Module):
             if not torch.jit.is_scripting():
                 h = self._layer_norm_eager(h, False)
             else:
-                h = self.layer_norm(h)
+                h = self._layer_norm_scripted(h)
         return h, c
+
+    def _layer_norm_scripted(self, t: Tensor) -> Tensor:
+        """The layer's nn.LayerNorm on this package's kernel, for the scripted (inference) path."""
+        ln = self.layer_norm
+        assert ln is not None
+        return torch.ops.sru_b200.layer_norm(t, ln.weight, ln.bias, ln.eps)
 
     @torch.jit.unused
     def _layer_norm_eager(self, t: Tensor, before_projection: bool) -> Tensor:
@@ -319,10 +342,12 @@ class SRUCell(nn.Module):
         x = input if input.dim() == 2 else input.contiguous().view(-1, self.input_size)
         if not torch.jit.is_scripting():
             return self._compute_U_eager(x)
+        # scripted (inference) path: this package's GEMM through its registered operator; the operator itself
+        # hands operands it does not take (fp32, unaligned shapes) to the library product
         weight_proj = self.weight_proj
         if weight_proj is not None:
-            return x.mm(weight_proj).mm(self.weight)
-        return x.mm(self.weight)
+            x = torch.ops.sru_b200.gemm(x, weight_proj, None)
+        return torch.ops.sru_b200.gemm(x, self.weight, None)
 
     @torch.jit.unused
     def _compute_U_eager(self, x: Tensor) -> Tensor:
@@ -463,7 +488,7 @@ class SRU(nn.Module):
         lstc = []
         i = 0
         for rnn in self.rnn_lst:
-            h, c = rnn(prevx, c0_[i], mask_pad=mask_pad)
+            h, c = rnn.forward_native(prevx, c0_[i], mask_pad=mask_pad)
             prevx = h
             lstc.append(c)
             i += 1

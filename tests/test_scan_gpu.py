@@ -224,7 +224,7 @@ def test_pipelined_tilings(v, threads, stages):
 
 
 @pytest.mark.parametrize("ss", [4, 8, 32])
-@pytest.mark.parametrize("v,threads", [(1, 64), (2, 64), (4, 128)])
+@pytest.mark.parametrize("v,threads", [(1, 64), (2, 64), (4, 64)])
 def test_pad_flags_across_stages(v, threads, ss):
     """mask_pad reaches the kernels through the producer warp, one pipeline stage ahead: sequences that
     span many stages and several trips round a two-stage ring, several batch rows per tile (the last tile
@@ -436,3 +436,42 @@ def test_options_interface():
     assert _lib.get_option("fwd_v") == -1
     with pytest.raises(_lib.SruB200Error):
         _lib.set_option("no_such_option", 1)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("v", [1, 2])
+@pytest.mark.parametrize("shape", [
+    # L,  B,  d,  dirs, k, pad,    threads, stages, ss
+    (37,  6, 128, 1, 3, None,     128, None, None),
+    (71,  7, 64,  2, 3, "tail",   64,  2,    4),
+    (19,  3, 32,  2, 4, "random", 32,  3,    8),
+    (130, 2, 256, 1, 3, "random", 128, 2,    32),
+    (5,   9, 16,  2, 4, "tail",   64,  None, None),
+])
+def test_split_role_forward(shape, v, dtype):
+    """The forward kernel with the state chain and the output work on separate warps: against the oracle, and bit
+    for bit against the one-role pipelined kernel (same operations per column), with and without a state history."""
+    from sru_b200 import _lib
+    ops = _ops()
+    L, B, d, dirs, k, pad, threads, stages, ss = shape
+    inp = random_inputs(L, B, d, dirs, k, pad=pad, scale=1.3, seed=L * 17 + B + v)
+    with _opts(fwd_split=1, fwd_v=v, scan_threads=threads, scan_stages=stages, scan_ss=ss):
+        out, ref = run_both(inp, dtype, expect_kernel=("split", "pipelined"))
+        compare(out, ref, TOL[dtype], ("split", shape, v, dtype))
+    (U, x, wc, bias, c0, mc, mp, gh, gl, *_r) = inp
+    dev = "cuda:0"
+    skip = 1 if k == 3 else 2
+    args = (U.to(dtype).to(dev), x.to(dtype).to(dev) if skip == 1 else None, wc.to(dev), bias.to(dev), c0.to(dev),
+            mc.to(dev), None if mp is None else mp.to(dev), L, B, d, dirs, k, 0, skip, 0, 1.3)
+    for hist in (True, False):
+        with _opts(fwd_split=1, fwd_v=v, scan_threads=threads, scan_stages=stages, scan_ss=ss):
+            a = ops.scan_forward(*args, hist)
+            assert _lib.last_scan_kernel() == "split"
+        with _opts(fwd_split=0, fwd_v=v, scan_threads=threads, scan_stages=stages, scan_ss=ss):
+            b = ops.scan_forward(*args, hist)
+            assert _lib.last_scan_kernel() == "pipelined"
+        assert torch.equal(a[0], b[0]) and torch.equal(a[2], b[2])
+        if hist:
+            assert torch.equal(a[1], b[1])
+    torch.cuda.synchronize()
+    _lib.check_device_error()
