@@ -243,6 +243,24 @@ int sru_b200_gemm_ws(
     void *workspace, size_t workspace_bytes, void *stream);
 
 /*
+ * The same contraction for float32 operands and a float32 result, still on the 16-bit tensor cores: each operand
+ * is split into three bfloat16 pieces and the six significant partial products are accumulated in fp32 by ONE
+ * bf16 GEMM over a six-fold reduction length (error about 2^-24 relative per product, i.e. float32 level).  This
+ * is what SRUCell.compute_U's `x.mm(weight)` (sru/modules.py:363-378) is for float32 tensors, where the reference
+ * calls the library's float32 GEMM.  M, N, K and ldc must be multiples of 8; `workspace` (256-byte aligned,
+ * ..._f32_workspace_bytes() bytes: three times the operands' size plus the inner product's own scratch) holds the
+ * stacked 16-bit operands.  Leading dimensions lda / ldb are those of the float32 matrices, in elements.
+ */
+size_t sru_b200_gemm_f32_workspace_bytes(int64_t m, int64_t n, int64_t k_dim);
+
+int sru_b200_gemm_f32(
+    float *c, const float *a, const float *b, const float *col_bias,
+    int64_t m, int64_t n, int64_t k_dim,
+    int64_t lda, int64_t ldb, int64_t ldc,
+    int trans_a, int trans_b, int accumulate,
+    void *workspace, size_t workspace_bytes, void *stream);
+
+/*
  * Layer normalisation over the last dimension: the nn.LayerNorm an SRU layer applies to its input
  * (sru/modules.py:252-253) or to its output (:278-279; constructed at :155-160 with the default
  * eps 1e-5 and an affine weight and bias).  In the reference this is a library operator (ATen's

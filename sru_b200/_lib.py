@@ -62,6 +62,10 @@ def lib():
         l.sru_b200_gemm_workspace_bytes.argtypes = [_i64, _i64, _i64, _int]
         l.sru_b200_gemm_ws.restype = _int
         l.sru_b200_gemm_ws.argtypes = [_vp] * 4 + [_i64] * 6 + [_int] * 5 + [_vp, ctypes.c_size_t, _vp]
+        l.sru_b200_gemm_f32_workspace_bytes.restype = ctypes.c_size_t
+        l.sru_b200_gemm_f32_workspace_bytes.argtypes = [_i64, _i64, _i64]
+        l.sru_b200_gemm_f32.restype = _int
+        l.sru_b200_gemm_f32.argtypes = [_vp] * 4 + [_i64] * 6 + [_int] * 3 + [_vp, ctypes.c_size_t, _vp]
         l.sru_b200_layer_norm_forward.restype = _int
         l.sru_b200_layer_norm_forward.argtypes = [_vp] * 6 + [_i64, _i64, ctypes.c_double, _int, _int, _vp]
         l.sru_b200_layer_norm_backward_workspace_bytes.restype = ctypes.c_size_t

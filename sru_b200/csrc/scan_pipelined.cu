@@ -154,12 +154,11 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const __grid_constant__ Sca
     const uint32_t x_off = u_region + r * x_slab + hc * sizeof(T);
     const uint32_t pad_off = u_region + x_region + r * SS;       // this row's flags of the stage
 
-    // With two or more columns per thread the inputs of a step are requested one step ahead (software pipeline of
-    // depth one within a stage): up_n / xp_n hold the packs of the NEXT step while the current one is computed.
-    // Measured on B200 (one 2048-wide layer, L = 1000): V = 4 at batch 256 0.875 -> 0.948 of the HBM peak, V = 2 at
-    // batch 32 0.76 -> 0.84; one column per thread (16 K columns) lost 30 % with it, and so did the backward kernel
-    // (its four packs per step cost 40 registers and with them a resident CTA per SM), so those fetch at the step.
-    constexpr bool kAhead = (V >= 2);
+    // The step's packs are fetched at the step.  Requesting them one step ahead (a software pipeline of depth one)
+    // was measured on B200: timed alone at full clocks it gained 4-8 % for two and four columns per thread, but inside
+    // the power-capped training step (SM clock ~1.2-1.35 GHz) the 50 extra registers cost more in resident warps than
+    // the earlier loads gained (2048-wide layer, L = 1000, batch 256: 16.8 ms -> 19.4-21.1 ms per step), and one
+    // column per thread lost 30 % everywhere.  Not done.
     Pack<T, V * K> up_n;
     Pack<T, V> xp_n;
     auto slab_of = [&](int j) { return asc ? j : SS - 1 - j; };   // j-th step of a stage in scan order
@@ -175,10 +174,9 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const __grid_constant__ Sca
         for (int ts = 0; ts < kTS; ++ts) {
             if (!FULL && ts >= steps) break;
             const bool pad = PAD && ((pad_bits >> (8 * ts)) & 0xffu);
-            if (!kAhead) fetch(sb, q + ts);
+            fetch(sb, q + ts);
             const Pack<T, V * K> up = up_n;
             const Pack<T, V> xp = xp_n;
-            if (kAhead && q + ts + 1 < SS) fetch(sb, q + ts + 1);    // the slab exists in the stage even past the sequence end
             float hv[V];
 #pragma unroll
             for (int i = 0; i < V; ++i) {
@@ -217,7 +215,6 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const __grid_constant__ Sca
                 break;
             }
             const uint32_t sb = order_after_wait(smem_u32(stage0) + (uint32_t)s * stage_bytes);
-            if (kAhead && active) fetch(sb, 0);
             for (int q = 0; q < SS && n < L; q += kTS, n += kTS) {
                 if (active) {
                     // the block's four flags, byte ts = scan step ts of the block
@@ -373,7 +370,8 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const __grid_constant__ Sca
         const uint32_t g_off = u_region + x_region + c_region + r * g_slab + hc * sizeof(T);
         const uint32_t pad_off = in_region + r * SS;                 // this row's flags of the stage
 
-        // The step's packs (fetched at the step: see the forward kernel for why not one step ahead).
+        // The step's packs (fetched at the step: see the forward kernel for why not one step ahead; the backward lost
+        // a resident CTA per SM to the 40 extra registers and 30 % of its throughput).
         Pack<T, V * K> up_n;
         Pack<T, V> gh_n, xp_n;
         Pack<TC, V> cp_n;
@@ -594,7 +592,12 @@ static bool choose_tile(int64_t L, int64_t B, int64_t d, int dirs, int k, int sk
         else { v = 2; ntc = 128; }
     }
     while (ntc > 32 && ncols / ((int64_t)v * ntc) < (int64_t)sms / 2) ntc /= 2;   // tiny problems: spread over the SMs
-    if (split) v = std::min(v, 2);
+    if (split) {
+        // measured on B200 (16-bit storage): one column per thread and two chain warps per CTA below ten column-warps
+        // per SM (16 K columns: 0.65 of the HBM peak against 0.43 for the one-role kernel), two columns and four chain
+        // warps from there on (64 K columns: 0.73-0.86 against 0.67-0.72)
+        if (w < 10) { v = 1; ntc = 64; } else { v = 2; ntc = 128; }
+    }
     v = option(backward ? OPT_BWD_V : OPT_FWD_V, v);
     if (v < vmin || v > (split ? 2 : vmax) || (v & (v - 1))) return false;
     ntc = option(OPT_SCAN_THREADS, ntc);
@@ -730,7 +733,13 @@ int launch_scan_pipelined(const ScanArgs &a, bool backward, cudaStream_t st) {
     if (!backward) {
         const int forced = option(OPT_FWD_SPLIT, -1);
         const int64_t w = a.B * (int64_t)a.d * a.dirs / (32 * (int64_t)num_sms());
-        split = forced < 0 ? (w < 10) : (forced != 0);
+        // By default (measured inside the benchmark steps, both kernels on one box): 16-bit storage, k = 3, and either
+        // fewer than ten column-warps per SM (16 K columns: 0.62 of the HBM peak against 0.42 for the one-role kernel)
+        // or fewer than twenty without a pad mask (64 K columns, 2048 wide: 0.86 against 0.70).  With a pad mask at
+        // 64 K columns the one-role kernel is ahead (0.81 against 0.66), with more warps it hides its latencies by
+        // itself (0.74 against 0.47 at 28 warps), and the k = 4 form was slower at every size.
+        split = forced < 0 ? (a.k == 3 && dtype_size(a.dtype) == 2 && (w < 10 || (w < 20 && a.mask_pad == nullptr)))
+                           : (forced != 0);
         if (split && !choose_tile(a.L, a.B, a.d, a.dirs, a.k, a.skip_type, a.dtype, a.c_dtype, false,
                                   a.mask_pad != nullptr, true, &p.c))
             split = false;

@@ -2,9 +2,10 @@
 
 16-bit operands (bf16 / fp16, e.g. under autocast) run on this package's tcgen05 GEMM
 (``sru_b200_gemm`` of the C ABI): forward ``U = x W``, backward ``grad_x = grad_U W^T`` and
-``grad_W = x^T grad_U``, all with fp32 accumulation in tensor memory.  fp32 / fp64 operands
-have no tensor-core path that keeps full precision, so they are a plain library GEMM
-(``torch.mm``).
+``grad_W = x^T grad_U``, all with fp32 accumulation in tensor memory.  float32 operands CAN run on the
+same GEMM through a three-way bfloat16 split (``sru_b200_gemm_f32``, ``set_fp32_on_tensor_cores``);
+by default they, float64 and odd shapes are a plain library GEMM (``torch.mm``), because the
+split product's accuracy (2e-6 ... 2e-5) does not meet the 1e-5 float32 parity bar for long reductions.
 """
 import os
 from typing import Optional
@@ -71,6 +72,68 @@ def gemm(a: Tensor, b: Tensor, trans_a: bool = False, trans_b: bool = False,
             _lib.DTYPE_CODE[a.dtype], _lib.DTYPE_CODE[out.dtype], int(accumulate),
             _lib.ptr(ws), ws_bytes, _lib.current_stream_ptr(a.device))
     return out
+
+
+def gemm_f32(a: Tensor, b: Tensor, trans_a: bool = False, trans_b: bool = False,
+             col_bias: Optional[Tensor] = None, name: Optional[str] = None) -> Tensor:
+    """C = op(a) @ op(b) for float32 CUDA matrices on the 16-bit tensor cores (``sru_b200_gemm_f32``: three-way
+    bfloat16 split of both operands, six partial products in one GEMM, fp32 accumulation).  All three extents must
+    be multiples of 8."""
+    if a.dtype != torch.float32 or b.dtype != torch.float32:
+        raise _lib.SruB200Error("gemm_f32 operands must be float32")
+    a = a if a.stride(1) == 1 else a.contiguous()
+    b = b if b.stride(1) == 1 else b.contiguous()
+    m = a.size(1) if trans_a else a.size(0)
+    kd = a.size(0) if trans_a else a.size(1)
+    n = b.size(0) if trans_b else b.size(1)
+    out = torch.empty(m, n, dtype=torch.float32, device=a.device)
+    if m == 0 or n == 0:
+        return out
+    bias = None if col_bias is None else col_bias.detach().float().contiguous()
+    L = _lib.lib()
+    with torch.cuda.device(a.device):
+        ws_bytes = int(L.sru_b200_gemm_f32_workspace_bytes(m, n, kd))
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device)
+        if name is None:
+            name = "gemm_wgrad" if trans_a else ("gemm_dgrad" if trans_b else "gemm_fwd")
+        _lib.call(name, 3, L.sru_b200_gemm_f32, _lib.ptr(out), _lib.ptr(a), _lib.ptr(b), _lib.ptr(bias), m, n, kd,
+                  a.stride(0), b.stride(0), out.stride(0), int(trans_a), int(trans_b), 0, _lib.ptr(ws), ws_bytes,
+                  _lib.current_stream_ptr(a.device))
+    return out
+
+
+_fp32_tensor = False
+
+
+def set_fp32_on_tensor_cores(flag: bool) -> None:
+    """float32 projections on the tcgen05 GEMM through the three-way bfloat16 split, or (default) on the library's
+    float32 GEMM (``torch.mm``).  Off by default because of accuracy: the tensor cores do not round their fp32
+    accumulation like IEEE additions, and the measured error of the split product is 2e-6 of the largest element at
+    K = 128 and 2e-5 at K = 2048 (library float32 GEMM: 5e-7 / 2e-6) -- above the 1e-5 parity bar for long
+    reductions, and above the reference's own 1e-4 absolute test bound on gradients of magnitude ~100."""
+    global _fp32_tensor
+    _fp32_tensor = bool(flag)
+
+
+def fp32_on_tensor_cores() -> bool:
+    return _fp32_tensor
+
+
+class _ProjectionF32(Function):
+    """x (M, K) @ w (K, N), all float32, forward and both gradients through gemm_f32."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        return gemm_f32(x, w)
+
+    @staticmethod
+    def backward(ctx, grad_u):
+        x, w = ctx.saved_tensors
+        grad_u = grad_u.contiguous().float()
+        gx = gemm_f32(grad_u, w, trans_b=True) if ctx.needs_input_grad[0] else None
+        gw = gemm_f32(x, grad_u, trans_a=True) if ctx.needs_input_grad[1] else None
+        return gx, gw
 
 
 _grad_link_on = True
@@ -212,7 +275,12 @@ def project(x: Tensor, w: Tensor, col_bias: Optional[Tensor] = None,
             link.armed = xc is x and x.requires_grad and torch.is_grad_enabled()
         with torch.autocast("cuda", enabled=False):
             return _Projection.apply(xc, w, col_bias, link if link is not None and link.armed else None)
-    out = x.mm(w) if x.dtype == w.dtype or torch.is_autocast_enabled("cuda") else x.to(dt).mm(w)
+    if (_fp32_tensor and gemm_backend() == "tcgen05" and x.dtype == torch.float32 and w.dtype == torch.float32
+            and not torch.is_autocast_enabled("cuda") and x.dim() == 2 and x.size(0) % 8 == 0 and x.size(1) % 8 == 0
+            and w.size(1) % 8 == 0 and x.size(0) > 0):
+        out = _ProjectionF32.apply(x.contiguous(), w.contiguous())
+    else:
+        out = x.mm(w) if x.dtype == w.dtype or torch.is_autocast_enabled("cuda") else x.to(dt).mm(w)
     if col_bias is not None:
         out = out + col_bias.to(out.dtype)
     return out

@@ -186,3 +186,36 @@ def test_first_layer_products_full_size():
     check_parity("gemm 120x8192x256000 wgrad", "grad_W cols", gw[:, cols], ref, 1e-3)
     torch.cuda.synchronize()
     _lib.check_device_error()
+
+
+@pytest.mark.parametrize("layout", ["nn", "nt", "tn"])
+@pytest.mark.parametrize("size", [(640, 384, 128), (256, 512, 2048), (8, 8, 8), (1000, 264, 72)])
+def test_gemm_f32_split_accuracy(size, layout):
+    """float32 product through the three-way bfloat16 split against a float64 product.  The split itself is exact to
+    2^-24, but the tensor cores' fp32 accumulation is not rounded like IEEE additions: the error grows with the
+    reduction length (3e-6 of the largest element up to K = 128, 3e-5 up to K = 2048; the library's float32 GEMM on
+    the same data is recorded beside it).  That is why this path is opt-in."""
+    from conftest import record_parity
+    from sru_b200.projection import gemm_f32
+    M, N, K = size
+    g = torch.Generator().manual_seed(M + 3 * K)
+    ta, tb = layout[0] == "t", layout[1] == "t"
+    a = torch.randn((K, M) if ta else (M, K), generator=g).to(DEV)
+    b = torch.randn((N, K) if tb else (K, N), generator=g).to(DEV)
+    bias = torch.randn(N, generator=g).to(DEV)
+    out = gemm_f32(a, b, trans_a=ta, trans_b=tb, col_bias=bias)
+    A, B = (a.t() if ta else a).double(), (b.t() if tb else b).double()
+    ref = A @ B + bias.double()
+    prior = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        lib32 = (a.t() if ta else a) @ (b.t() if tb else b) + bias
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prior
+    e, e_lib = rel_err(out, ref), rel_err(lib32, ref)
+    tol = 3e-6 if K <= 128 else 3e-5
+    record_parity("gemm_f32 %s %s" % (size, layout), "C", e, tol, "library fp32 GEMM: %.1e" % e_lib)
+    assert e <= tol, (e, e_lib)
+    from sru_b200 import _lib
+    torch.cuda.synchronize()
+    _lib.check_device_error()
