@@ -361,7 +361,7 @@ def main():
 
     import torch.distributed as dist
     from sru_b200 import _lib, ops
-    from sru_b200.distributed import LayerGradAllReducer, shard_batch
+    from sru_b200.distributed import LayerGradAllReducer, shard_batch, use_global_dropout_masks
     from sru_b200.projection import gemm_backend
     _lib.lib()  # fail loudly here if the native library is missing
     if args.no_bias_fold:
@@ -377,6 +377,9 @@ def main():
         sys.stderr.write("warning: --gpus %d but WORLD_SIZE %d\n" % (args.gpus, world))
 
     model = build_model(cfg, device)
+    if cfg["train"] and cfg["kwargs"].get("dropout", 0) > 0:
+        # every rank draws the masks of the global batch and keeps its rows: the step computes the same numbers at every N
+        use_global_dropout_masks(model, cfg["B"], rank, world, seed=1234)
     x_cpu, mask_cpu = make_inputs(cfg, args.config, cfg["B"])
     x_cpu = shard_batch(x_cpu, rank, world)
     mask_cpu = shard_batch(mask_cpu, rank, world)

@@ -36,6 +36,33 @@ def shard_batch(t: Optional[torch.Tensor], rank: int, world: int, dim: int = 1) 
     return t.narrow(dim, start, base + (1 if rank < rem else 0)).contiguous()
 
 
+def use_global_dropout_masks(model: nn.Module, global_batch: int, rank: int, world: int, seed: int = 0) -> None:
+    """Makes the sharded step draw exactly the dropout masks of the single-process step.
+
+    The reference draws a layer's mask for the whole batch (sru/modules.py:380-387).  With the batch split across
+    ranks, each rank would draw its own, different numbers, and the sharded step would no longer compute what the
+    single-process step computes.  After this call every layer draws its mask for the GLOBAL batch from a generator
+    that is seeded identically on every rank (seed, layer index, number of draws so far) and keeps the rows of this
+    rank's shard, so losses and gradients agree across world sizes up to summation order.  Also valid at world 1.
+    """
+    base, rem = divmod(global_batch, world)
+    start = rank * base + min(rank, rem)
+    rows = base + (1 if rank < rem else 0)
+    for li, cell in enumerate(getattr(model, "rnn_lst", [])):
+        state = {"draws": 0}
+
+        def draw(size, p, _cell=cell, _li=li, _state=state):
+            like = _cell.bias.data
+            gen = torch.Generator(device=like.device)
+            gen.manual_seed(seed * 1000003 + _li * 10007 + _state["draws"])
+            _state["draws"] += 1
+            full = like.new_empty((global_batch, size[1])).bernoulli_(1 - p, generator=gen).div_(1 - p)
+            if size[0] != rows:
+                raise ValueError("dropout mask for %d rows requested, this rank's shard has %d" % (size[0], rows))
+            return full[start:start + rows].contiguous()
+        cell.get_dropout_mask_ = draw
+
+
 class LayerGradAllReducer:
     """Per-layer bucketed gradient all-reduce (SUM) overlapped with backward.
 

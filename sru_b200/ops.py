@@ -201,6 +201,7 @@ class ElementwiseRecurrence(Function):
                 has_skip_term, scale_x, mask_c=None, mask_pad=None, grad_link=None, bias_in_u=False):
         length, batch, dirs, k, skip_type, is_custom = _geometry(u, x, d_out, bidirectional,
                                                                  has_skip_term, weight_c)
+        ctx.set_materialize_grads(False)    # no zero tensor is built for the (usually unused) gradient of the final state
         st = u.dtype
         sm = _small_dtype(st)
         D = d_out * dirs
@@ -238,7 +239,12 @@ class ElementwiseRecurrence(Function):
         D = d * dirs
         st = u.dtype
         sm = _small_dtype(st)
-        gh = grad_h.to(st).contiguous().view(length, batch, D)
+        # gradients autograd did not produce arrive as None (set_materialize_grads(False) in forward): the kernel takes
+        # a null grad_last as zeros, and a missing grad_h (only the final state was used) becomes zeros here
+        if grad_h is None:
+            gh = torch.zeros(length, batch, D, dtype=st, device=u.device)
+        else:
+            gh = grad_h.to(st).contiguous().view(length, batch, D)
         gl = _prep_small(grad_last, sm)
         grad_u, grad_x, grad_wc, grad_bias, grad_init = scan_backward(
             u.view(length, batch, D * k), x, wc, bias, init, mask_c, pad, c_hist, gh, gl,
