@@ -5,6 +5,7 @@
 
 #include <type_traits>
 
+#include "f32x2.cuh"
 #include "scan.cuh"
 
 namespace srub {
@@ -68,6 +69,14 @@ template <int MODE> struct Gate {
     static constexpr bool kPair = (MODE == 0);   // eval_pair delivers the complement
 };
 template <typename T> using GateFor = Gate<sizeof(T) == 4 ? 0 : 2>;
+
+// The 16-bit-storage gate (MODE 2) on a pair of columns: 0.5 * tanh(c * wcf + (u * 0.5 + bf)) + 0.5 with the same
+// four roundings per lane as Gate<2>::eval.
+__device__ __forceinline__ F2 gate2_pair(F2 c, F2 wcf, F2 u, F2 bf, F2 half) {
+    float lo, hi;
+    f2_split(f2_fma(c, wcf, f2_fma(u, half, bf)), lo, hi);
+    return f2_fma(f2_make(tanh_approx(lo), tanh_approx(hi)), half, half);
+}
 
 // float[N] -> Pack<T,N>, two values per conversion instruction for the 16-bit types.
 template <typename T, int N> __device__ __forceinline__ void pack_from_float(Pack<T, N> &out, const float (&v)[N]) {

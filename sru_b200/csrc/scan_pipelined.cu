@@ -154,42 +154,40 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const __grid_constant__ Sca
     const uint32_t x_off = u_region + r * x_slab + hc * sizeof(T);
     const uint32_t pad_off = u_region + x_region + r * SS;       // this row's flags of the stage
 
-    // The step's packs are fetched at the step.  Requesting them one step ahead (a software pipeline of depth one)
+    // A step's packs are loaded at the step.  Requesting them one step ahead (a software pipeline of depth one)
     // was measured on B200: timed alone at full clocks it gained 4-8 % for two and four columns per thread, but inside
     // the power-capped training step (SM clock ~1.2-1.35 GHz) the 50 extra registers cost more in resident warps than
     // the earlier loads gained (2048-wide layer, L = 1000, batch 256: 16.8 ms -> 19.4-21.1 ms per step), and one
     // column per thread lost 30 % everywhere.  Not done.
-    Pack<T, V * K> up_n;
-    Pack<T, V> xp_n;
-    auto slab_of = [&](int j) { return asc ? j : SS - 1 - j; };   // j-th step of a stage in scan order
-    auto fetch = [&](uint32_t sb, int j) {
-        up_n = lds_pack<Pack<T, V * K>>(sb + u_off + slab_of(j) * su);
-        if (has_x) xp_n = lds_pack<Pack<T, V>>(sb + x_off + slab_of(j) * sx);
-    };
+    const int dsu = asc ? su : -su, dsx = asc ? sx : -sx;   // bytes to the next step's slab in scan order
+    // (the packed two-columns-per-instruction arithmetic of the backward kernel was measured here too: no gain, the
+    // forward pass is not issue-bound: 16.0 vs 16.3-16.5 ms per step of the 12-layer benchmark)
 
-    // One block of kTS steps starting q steps into the stage.
-    auto block = [&](uint32_t sb, int q, uint32_t pad_bits, int steps, auto pad_c, auto hist_c, auto full_c) {
+    // One block of kTS steps.  ub / xb point at this thread's slice in the slab of the block's first step.
+    auto block = [&](uint32_t ub, uint32_t xb, uint32_t pad_bits, int steps, auto pad_c, auto hist_c, auto full_c) {
         constexpr bool PAD = decltype(pad_c)::value, HIST = decltype(hist_c)::value, FULL = decltype(full_c)::value;
 #pragma unroll
         for (int ts = 0; ts < kTS; ++ts) {
             if (!FULL && ts >= steps) break;
             const bool pad = PAD && ((pad_bits >> (8 * ts)) & 0xffu);
-            fetch(sb, q + ts);
-            const Pack<T, V * K> up = up_n;
-            const Pack<T, V> xp = xp_n;
+            const Pack<T, V * K> up = lds_pack<Pack<T, V * K>>(ub + ts * dsu);
+            Pack<T, V> xp;
+            if (has_x) xp = lds_pack<Pack<T, V>>(xb + ts * dsx);
             float hv[V];
+            {
 #pragma unroll
-            for (int i = 0; i < V; ++i) {
-                const float u0 = Cvt<T>::to_f(up.v[i * K + 0]);
-                const float u1 = Cvt<T>::to_f(up.v[i * K + 1]);
-                const float u2 = Cvt<T>::to_f(up.v[i * K + 2]);
-                const float xv = (K == 4) ? Cvt<T>::to_f(up.v[i * K + K - 1]) : Cvt<T>::to_f(xp.v[i]) * scale;
-                const float g1 = G::eval(c[i], wc1n[i], u1, b1n[i]);
-                const float g2 = G::eval(c[i], wc2n[i], u2, b2n[i]);
-                const float cn = fmaf(c[i] - u0, g1, u0);
-                const float hn = fmaf((cn - xv) * mk[i], g2, xv);
-                c[i] = pad ? c[i] : cn;
-                hv[i] = pad ? 0.f : hn;
+                for (int i = 0; i < V; ++i) {
+                    const float u0 = Cvt<T>::to_f(up.v[i * K + 0]);
+                    const float u1 = Cvt<T>::to_f(up.v[i * K + 1]);
+                    const float u2 = Cvt<T>::to_f(up.v[i * K + 2]);
+                    const float xv = (K == 4) ? Cvt<T>::to_f(up.v[i * K + K - 1]) : Cvt<T>::to_f(xp.v[i]) * scale;
+                    const float g1 = G::eval(c[i], wc1n[i], u1, b1n[i]);
+                    const float g2 = G::eval(c[i], wc2n[i], u2, b2n[i]);
+                    const float cn = fmaf(c[i] - u0, g1, u0);
+                    const float hn = fmaf((cn - xv) * mk[i], g2, xv);
+                    c[i] = pad ? c[i] : cn;
+                    hv[i] = pad ? 0.f : hn;
+                }
             }
             Pack<T, V> ho;
             pack_from_float(ho, hv);
@@ -219,9 +217,11 @@ __global__ void __launch_bounds__(160) scan_fwd_pipe(const __grid_constant__ Sca
                 if (active) {
                     // the block's four flags, byte ts = scan step ts of the block
                     const uint32_t pad_cur = PADF ? pad_word(sb + pad_off, q, SS, asc) : 0u;
+                    const int slab = asc ? q : (SS - 1 - q);
+                    const uint32_t ub = sb + u_off + slab * su, xb = sb + x_off + slab * sx;
                     const int64_t left = L - n;
-                    if (left >= kTS) block(sb, q, pad_cur, kTS, pad_c, hist_c, BoolC<true>{});
-                    else block(sb, q, pad_cur, (int)left, pad_c, hist_c, BoolC<false>{});
+                    if (left >= kTS) block(ub, xb, pad_cur, kTS, pad_c, hist_c, BoolC<true>{});
+                    else block(ub, xb, pad_cur, (int)left, pad_c, hist_c, BoolC<false>{});
                 }
             }
             __syncwarp();
@@ -370,35 +370,84 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const __grid_constant__ Sca
         const uint32_t g_off = u_region + x_region + c_region + r * g_slab + hc * sizeof(T);
         const uint32_t pad_off = in_region + r * SS;                 // this row's flags of the stage
 
-        // The step's packs (fetched at the step: see the forward kernel for why not one step ahead; the backward lost
-        // a resident CTA per SM to the 40 extra registers and 30 % of its throughput).
-        Pack<T, V * K> up_n;
-        Pack<T, V> gh_n, xp_n;
-        Pack<TC, V> cp_n;
-        auto slab_of = [&](int j) { return asc ? j : SS - 1 - j; };
-        auto fetch = [&](uint32_t sb, int j) {
-            const int sl = slab_of(j);
-            up_n = lds_pack<Pack<T, V * K>>(sb + u_off + sl * su);
-            gh_n = lds_pack<Pack<T, V>>(sb + g_off + sl * sg);
-            if (has_x) xp_n = lds_pack<Pack<T, V>>(sb + x_off + sl * sx);
-            cp_n = lds_pack<Pack<TC, V>>(sb + c_off + sl * sc);
-        };
+        // (packs are loaded at the step: see the forward kernel for why not one step ahead; the backward lost a resident
+        // CTA per SM to the 40 extra registers and 30 % of its throughput)
+        const int dsu = asc ? su : -su, dsx = asc ? sx : -sx, dsc = asc ? sc : -sc, dsg = asc ? sg : -sg;
+        // 16-bit storage (tanh gates): a thread's columns are processed in PAIRS with the packed float32 instructions
+        // of f32x2.cuh.  Measured inside the 12-layer training step, both builds on one box: 26.5-27.0 -> 24.6-24.7 ms
+        // per step (0.78-0.80 -> 0.86 of the HBM peak at an SM clock of 1.2-1.35 GHz, where the kernel is issue-bound).
+        constexpr bool kPairs = (sizeof(T) == 2) && (V % 2 == 0);
 
-        // One block of kTS steps starting q steps into the stage.  LAST marks the final block (ragged, and holding
-        // the step whose predecessor state is c_init); all other blocks are full and branch-free.
-        auto block = [&](uint32_t sb, int q, uint32_t pad_bits, int steps, auto pad_c, auto last_c) {
+        // One block of kTS steps; ub / xb / cb / gb point at this thread's slices in the slab of the block's first step.
+        // LAST marks the final block (ragged, and holding the step whose predecessor state is c_init); all other
+        // blocks are full and branch-free.
+        auto block = [&](uint32_t ub, uint32_t xb, uint32_t cb, uint32_t gb, uint32_t pad_bits, int steps, auto pad_c,
+                         auto last_c) {
             constexpr bool PAD = decltype(pad_c)::value, LAST = decltype(last_c)::value;
 #pragma unroll
             for (int ts = 0; ts < kTS; ++ts) {
                 if (LAST && ts >= steps) break;
                 const bool pad = PAD && ((pad_bits >> (8 * ts)) & 0xffu);
                 const bool at_start = LAST && (ts == steps - 1);
-                fetch(sb, q + ts);
-                const Pack<T, V * K> up = up_n;
-                const Pack<T, V> ghp = gh_n;
-                const Pack<T, V> xp = xp_n;
-                const Pack<TC, V> cpp = cp_n;
+                const Pack<T, V * K> up = lds_pack<Pack<T, V * K>>(ub + ts * dsu);
+                const Pack<T, V> ghp = lds_pack<Pack<T, V>>(gb + ts * dsg);
+                Pack<T, V> xp;
+                if (has_x) xp = lds_pack<Pack<T, V>>(xb + ts * dsx);
+                const Pack<TC, V> cpp = lds_pack<Pack<TC, V>>(cb + ts * dsc);
                 float guv[V * K], gxv_[V];
+                if constexpr (kPairs) {
+                    // two columns per instruction (f32x2.cuh).  Same formulas as the scalar form below; 1 - g is formed
+                    // explicitly (the packed instructions take no negated operand), which moves a rounding or two but
+                    // nothing a 16-bit output can show.
+                    const F2 half = f2_splat(0.5f), one = f2_splat(1.f), scale2 = f2_splat(scale), unfold = f2_splat(G::kUnfold);
+#pragma unroll
+                    for (int i = 0; i < V; i += 2) {
+                        const F2 u0 = f2_make(Cvt<T>::to_f(up.v[i * K + 0]), Cvt<T>::to_f(up.v[(i + 1) * K + 0]));
+                        const F2 u1 = f2_make(Cvt<T>::to_f(up.v[i * K + 1]), Cvt<T>::to_f(up.v[(i + 1) * K + 1]));
+                        const F2 u2 = f2_make(Cvt<T>::to_f(up.v[i * K + 2]), Cvt<T>::to_f(up.v[(i + 1) * K + 2]));
+                        F2 xv;
+                        if (K == 4) xv = f2_make(Cvt<T>::to_f(up.v[i * K + K - 1]), Cvt<T>::to_f(up.v[(i + 1) * K + K - 1]));
+                        else xv = f2_mul(f2_make(Cvt<T>::to_f(xp.v[i]), Cvt<T>::to_f(xp.v[i + 1])), scale2);
+                        const F2 cprev = at_start ? f2_make(c0[i], c0[i + 1])
+                                                  : f2_make(Cvt<TC>::to_f(cpp.v[i]), Cvt<TC>::to_f(cpp.v[i + 1]));
+                        const F2 gh = f2_make(Cvt<T>::to_f(ghp.v[i]), Cvt<T>::to_f(ghp.v[i + 1]));
+                        const F2 wc1p = f2_make(wc1n[i], wc1n[i + 1]), wc2p = f2_make(wc2n[i], wc2n[i + 1]);
+                        const F2 g1 = gate2_pair(cprev, wc1p, u1, f2_make(b1n[i], b1n[i + 1]), half);
+                        const F2 g2 = gate2_pair(cprev, wc2p, u2, f2_make(b2n[i], b2n[i + 1]), half);
+                        const F2 dc = f2_sub(cprev, u0);
+                        const F2 cv = f2_fma(dc, g1, u0);
+                        const F2 ghm = f2_mul(gh, f2_make(mk[i], mk[i + 1]));
+                        const F2 curp = f2_make(cur[i], cur[i + 1]);
+                        const F2 gc = f2_fma(ghm, g2, curp);
+                        const F2 omg1 = f2_sub(one, g1), omg2 = f2_sub(one, g2);
+                        F2 gg2 = f2_mul(f2_mul(ghm, f2_sub(cv, xv)), f2_mul(g2, omg2));
+                        F2 gg1 = f2_mul(f2_mul(gc, dc), f2_mul(g1, omg1));
+                        F2 gu0 = f2_mul(gc, omg1);
+                        F2 gxv = f2_sub(gh, f2_mul(ghm, g2));
+                        const F2 curn = f2_fma(gc, g1, f2_mul(unfold, f2_fma(gg1, wc1p, f2_mul(gg2, wc2p))));
+                        if (PAD) {
+                            const F2 zero = f2_splat(0.f);
+                            gg1 = f2_select(pad, zero, gg1); gg2 = f2_select(pad, zero, gg2);
+                            gu0 = f2_select(pad, zero, gu0); gxv = f2_select(pad, zero, gxv);
+                        }
+                        float a0, a1;
+                        f2_split(f2_select(pad, curp, curn), a0, a1);
+                        cur[i] = a0; cur[i + 1] = a1;
+                        f2_split(f2_add(f2_make(gb1[i], gb1[i + 1]), gg1), a0, a1);
+                        gb1[i] = a0; gb1[i + 1] = a1;
+                        f2_split(f2_add(f2_make(gb2[i], gb2[i + 1]), gg2), a0, a1);
+                        gb2[i] = a0; gb2[i + 1] = a1;
+                        f2_split(f2_fma(gg1, cprev, f2_make(gwc1[i], gwc1[i + 1])), a0, a1);
+                        gwc1[i] = a0; gwc1[i + 1] = a1;
+                        f2_split(f2_fma(gg2, cprev, f2_make(gwc2[i], gwc2[i + 1])), a0, a1);
+                        gwc2[i] = a0; gwc2[i + 1] = a1;
+                        f2_split(gu0, guv[i * K + 0], guv[(i + 1) * K + 0]);
+                        f2_split(gg1, guv[i * K + 1], guv[(i + 1) * K + 1]);
+                        f2_split(gg2, guv[i * K + 2], guv[(i + 1) * K + 2]);
+                        if (K == 4) f2_split(gxv, guv[i * K + K - 1], guv[(i + 1) * K + K - 1]);
+                        f2_split(f2_mul(gxv, scale2), gxv_[i], gxv_[i + 1]);
+                    }
+                } else {
 #pragma unroll
                 for (int i = 0; i < V; ++i) {
                     const float u0 = Cvt<T>::to_f(up.v[i * K + 0]);
@@ -437,6 +486,7 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const __grid_constant__ Sca
                     if (K == 4) guv[i * K + K - 1] = gxv;
                     gxv_[i] = gxv * scale;
                 }
+                }
                 Pack<T, V * K> guo;
                 pack_from_float(guo, guv);
                 *reinterpret_cast<Pack<T, V * K> *>(gup) = guo;
@@ -464,9 +514,12 @@ __global__ void __launch_bounds__(160) scan_bwd_pipe(const __grid_constant__ Sca
                 for (int q = 0; q < SS && m < L; q += kTS, m += kTS) {
                     if (active) {
                         const uint32_t pad_cur = PADF ? pad_word(sb + pad_off, q, SS, asc) : 0u;
+                        const int slab = asc ? q : (SS - 1 - q);
+                        const uint32_t ub = sb + u_off + slab * su, xb = sb + x_off + slab * sx;
+                        const uint32_t cb = sb + c_off + slab * sc, gb = sb + g_off + slab * sg;
                         const int64_t left = L - m;   // steps left including this block
-                        if (left > kTS) block(sb, q, pad_cur, kTS, pad_c, BoolC<false>{});
-                        else block(sb, q, pad_cur, (int)left, pad_c, BoolC<true>{});
+                        if (left > kTS) block(ub, xb, cb, gb, pad_cur, kTS, pad_c, BoolC<false>{});
+                        else block(ub, xb, cb, gb, pad_cur, (int)left, pad_c, BoolC<true>{});
                     }
                 }
                 __syncwarp();
