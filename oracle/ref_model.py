@@ -155,6 +155,9 @@ class OracleSRU(nn.Module):
         # (U, x, V, bias, c0, activation_type, d, bidirectional, has_skip, scale_x, mask_c, mask_pad) -> (h, c_last);
         # the benchmark's forward-only CPU baseline puts the reference's compiled operator here
         self.recurrence: Callable = sru_oracle.elementwise_recurrence_oracle
+        # 16-bit checks: the oracle of a 16-bit run is the float32 recurrence fed the same 16-bit-rounded U, as the
+        # parity metric defines it (gradients stay unrounded)
+        self.round_u_to: Optional[torch.dtype] = None
 
     # ---- one layer: sru/modules.py:235-281 ----
     def _layer_forward(self, li: int, lay: _Layer, inp: torch.Tensor, c0: Optional[torch.Tensor],
@@ -188,6 +191,10 @@ class OracleSRU(nn.Module):
                 U, V = ret[0], ret[1] + lay.weight_c
             else:
                 U, V = ret, lay.weight_c
+        if self.round_u_to is not None:
+            # forward value only: a 16-bit cast in the autograd graph would also round grad_U, which underflows in
+            # fp16 when the oracle runs without the loss scale of the run it checks
+            U = U + (U.to(self.round_u_to).to(U.dtype) - U).detach()
         h, c = self.recurrence(
             U.to(real), skip_input.to(real), V.to(real), lay.bias.to(real), c0.to(real), lay.act, lay.d,
             lay.dirs == 2, lay.has_skip, None if scale is None else scale.to(real),
@@ -244,7 +251,8 @@ def from_state(kwargs: Dict, state: Dict[str, torch.Tensor], round_to: Optional[
     """An OracleSRU with the given reference-style constructor arguments and state dict.
 
     round_to: round every projection weight (``weight``, ``weight_proj``, ``input_to_hidden.weight``) to
-    this 16-bit type and back, the way a 16-bit autocast GEMM sees them; the model itself stays float32.
+    this 16-bit type and back, the way a 16-bit autocast GEMM sees them, and round each layer's U to it before the
+    recurrence (the GEMM's output type); the model itself stays float32.
     """
     kw = dict(kwargs)
     m = OracleSRU(kw.pop("input_size"), kw.pop("hidden_size"), **kw)
@@ -261,6 +269,7 @@ def from_state(kwargs: Dict, state: Dict[str, torch.Tensor], round_to: Optional[
                         and ".layer_norm." not in name:
                     src = src.to(round_to).to(t.dtype)
                 t.copy_(src)
+    m.round_u_to = round_to
     return m
 
 

@@ -178,7 +178,7 @@ def test_config4_full_size_through_the_module():
         h, c = model(xd)
     assert h.dtype == torch.bfloat16 and h.shape == (L, B, 1024) and c.shape == (1, B, 1024)
     rows = [2, 15]
-    ref = to_oracle(model).eval()
+    ref = to_oracle(model, round_to=torch.bfloat16).eval()
     with torch.no_grad():
         oh, oc = ref(xd[:, rows].float().cpu())
     check_parity("config4", "h", h[:, rows], oh, TOL16, "2 rows")
