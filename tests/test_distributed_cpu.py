@@ -11,7 +11,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from oracle.ref_model import OracleSRU
-from sru_b200.distributed import LayerGradAllReducer, shard_batch
+from sru_b200.distributed import LayerGradAllReducer, shard_batch, use_global_dropout_masks
 
 KW = dict(input_size=12, hidden_size=8, num_layers=3, bidirectional=True, layer_norm=True, rescale=True)
 L, B = 7, 5   # odd batch: ranks get 3 and 2 sequences
@@ -25,10 +25,17 @@ def _inputs():
     return x, mask
 
 
-def _model():
+def _model(dropout=0.0):
     torch.manual_seed(7)
-    kw = dict(KW)
+    kw = dict(KW, dropout=dropout)
     return OracleSRU(kw.pop("input_size"), kw.pop("hidden_size"), **kw).train()
+
+
+def _global_masks(model, rank, world):
+    """Dropout masks drawn for the global batch, identically on every rank (the oracle model asks its
+    ``mask_source``; the shipped layers ask ``get_dropout_mask_``, which is what the call installs)."""
+    use_global_dropout_masks(model, B, rank, world, seed=11)
+    model.mask_source = lambda li, like, size, p: model.rnn_lst[li].get_dropout_mask_(size, p)
 
 
 def _loss(h):
@@ -40,7 +47,9 @@ def _worker(rank, world, port, out, mode):
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     torch.set_num_threads(1)
-    model = _model()
+    model = _model(dropout=0.3 if mode == "global_dropout" else 0.0)
+    if mode == "global_dropout":
+        _global_masks(model, rank, world)
     x, mask = _inputs()
     xs, ms = shard_batch(x, rank, world), shard_batch(mask, rank, world)
     reducer = LayerGradAllReducer(model, reduce_dtype=torch.bfloat16 if mode == "bf16_wire" else None)
@@ -89,20 +98,26 @@ def test_shard_batch_covers_everything():
 
 
 @pytest.mark.parametrize("mode", ["plain", "optimizer_zero_grad", "no_zero_grad_rearm", "double_backward",
-                                  "frozen_param", "bf16_wire"])
+                                  "frozen_param", "bf16_wire", "global_dropout"])
 def test_two_rank_gradients_equal_single_process(tmp_path, mode):
     """Gradients after three steps on two ranks equal the single-process gradients of the whole batch:
     with the reducer's own zero_grad; with an optimizer's zero_grad(set_to_none=True), which detaches the
     gradients from the buckets; when only finish() re-arms the reducer; after a refused second backward;
-    with a parameter that receives no gradient; with the sum taken on a bf16 copy of the bucket."""
+    with a parameter that receives no gradient; with the sum taken on a bf16 copy of the bucket; with dropout
+    masks drawn for the global batch (every rank keeps its rows of the same mask, so the sharded step computes
+    what the single process computes)."""
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     out = str(tmp_path / "grads.pt")
     mp.spawn(_worker, args=(2, port, out, mode), nprocs=2, join=True)
     got = torch.load(out)
-    model = _model()
+    model = _model(dropout=0.3 if mode == "global_dropout" else 0.0)
     x, mask = _inputs()
+    if mode == "global_dropout":
+        _global_masks(model, 0, 1)
+        for _ in range(2):                  # the workers' third step uses each layer's third draw
+            model(x, mask_pad=mask)
     h, c = model(x, mask_pad=mask)
     _loss(h).backward()
     named = dict(model.named_parameters())
