@@ -41,25 +41,43 @@ def use_global_dropout_masks(model: nn.Module, global_batch: int, rank: int, wor
 
     The reference draws a layer's mask for the whole batch (sru/modules.py:380-387).  With the batch split across
     ranks, each rank would draw its own, different numbers, and the sharded step would no longer compute what the
-    single-process step computes.  After this call every layer draws its mask for the GLOBAL batch from a generator
-    that is seeded identically on every rank (seed, layer index, number of draws so far) and keeps the rows of this
-    rank's shard, so losses and gradients agree across world sizes up to summation order.  Also valid at world 1.
+    single-process step computes.  After this call the masks of ALL layers for the GLOBAL batch come from one draw
+    per step of a generator that is seeded identically on every rank (seed, number of draws so far), and every
+    layer keeps the rows of this rank's shard, so losses and gradients agree across world sizes up to summation
+    order.  Also valid at world 1.  Layers whose width or dropout probability differs from the first layer's draw
+    their own global mask the same way.
     """
     base, rem = divmod(global_batch, world)
     start = rank * base + min(rank, rem)
     rows = base + (1 if rank < rem else 0)
-    for li, cell in enumerate(getattr(model, "rnn_lst", [])):
-        state = {"draws": 0}
+    cells = list(getattr(model, "rnn_lst", []))
+    if not cells:
+        return
+    width0, p0 = cells[0].bias.numel() // 2, None
+    pools: Dict[int, torch.Tensor] = {}          # draw number -> (layers, global batch, width) masks
+    draws = [0] * len(cells)
 
-        def draw(size, p, _cell=cell, _li=li, _state=state):
+    def full_masks(like, n, width, p, k, salt):
+        gen = torch.Generator(device=like.device)
+        gen.manual_seed(seed * 1000003 + salt * 10007 + k)
+        return like.new_empty((n, global_batch, width)).bernoulli_(1 - p, generator=gen).div_(1 - p)
+
+    for li, cell in enumerate(cells):
+        def draw(size, p, _cell=cell, _li=li):
+            nonlocal p0
             like = _cell.bias.data
-            gen = torch.Generator(device=like.device)
-            gen.manual_seed(seed * 1000003 + _li * 10007 + _state["draws"])
-            _state["draws"] += 1
-            full = like.new_empty((global_batch, size[1])).bernoulli_(1 - p, generator=gen).div_(1 - p)
+            k = draws[_li]
+            draws[_li] += 1
             if size[0] != rows:
                 raise ValueError("dropout mask for %d rows requested, this rank's shard has %d" % (size[0], rows))
-            return full[start:start + rows].contiguous()
+            if p0 is None:
+                p0 = p
+            if size[1] != width0 or p != p0:      # an odd layer: its own global draw
+                return full_masks(like, 1, size[1], p, k, 1 + _li)[0, start:start + rows].contiguous()
+            if k not in pools:
+                pools.clear()                     # the previous step's masks are no longer needed
+                pools[k] = full_masks(like, len(cells), width0, p0, k, 0)
+            return pools[k][_li, start:start + rows]
         cell.get_dropout_mask_ = draw
 
 

@@ -248,7 +248,10 @@ class SRUCell(nn.Module):
         scale_val = self.scale_x if self.rescale else None
         mask_c: Optional[Tensor] = None
         if self.training and (self.dropout > 0):
-            mask_c = self.get_dropout_mask_((batch_size, self.output_size), self.dropout)
+            if not torch.jit.is_scripting():
+                mask_c = self._take_preset_mask(batch_size)
+            if mask_c is None:
+                mask_c = self.get_dropout_mask_((batch_size, self.output_size), self.dropout)
 
         if not torch.jit.is_scripting():
             self._begin_grad_link(input, residual)
@@ -369,6 +372,16 @@ class SRUCell(nn.Module):
         b = self.bias.data
         return b.new_empty(size).bernoulli_(1 - p).div_(1 - p)
 
+    @torch.jit.unused
+    def _take_preset_mask(self, batch_size: int) -> Optional[Tensor]:
+        """The mask an enclosing ``SRU`` drew for this layer and this call (all layers' masks come from one
+        launch there), or None."""
+        m = self.__dict__.get("_preset_mask_c")
+        if m is None:
+            return None
+        self.__dict__["_preset_mask_c"] = None
+        return m if m.shape == (batch_size, self.output_size) else None
+
     def extra_repr(self):
         parts = ["{}, {}".format(self.input_size, self.hidden_size)]
         if self.projection_size > 0:
@@ -485,6 +498,8 @@ class SRU(nn.Module):
             c0_ = [x.squeeze(0) for x in c0.chunk(self.num_layers, 0)]
 
         prevx = input if self.input_to_hidden is None else self.input_to_hidden(input)
+        if not torch.jit.is_scripting():
+            self._preset_dropout_masks(input.size(1))
         lstc = []
         i = 0
         for rnn in self.rnn_lst:
@@ -505,6 +520,25 @@ class SRU(nn.Module):
         if isinstance(orig_input, PackedSequence):
             prevx = nn.utils.rnn.pack_padded_sequence(prevx, lengths, enforce_sorted=False)
         return prevx, lstc_stack
+
+    @torch.jit.unused
+    def _preset_dropout_masks(self, batch_size: int) -> None:
+        """Draws the dropout masks of all layers with ONE bernoulli launch (the reference draws one per layer,
+        sru/modules.py:380-387; same distribution, two launches per step instead of two per layer).  Layers whose
+        ``get_dropout_mask_`` was replaced on the instance keep drawing their own."""
+        if not self.training:
+            return
+        cells = [c for c in self.rnn_lst if c.dropout > 0 and "get_dropout_mask_" not in c.__dict__]
+        if len(cells) < 2:
+            return
+        first = cells[0]
+        if any(c.dropout != first.dropout or c.output_size != first.output_size
+               or c.bias.device != first.bias.device or c.bias.dtype != first.bias.dtype for c in cells):
+            return
+        p = first.dropout
+        masks = first.bias.data.new_empty((len(cells), batch_size, first.output_size)).bernoulli_(1 - p).div_(1 - p)
+        for i, c in enumerate(cells):
+            c.__dict__["_preset_mask_c"] = masks[i]
 
     @torch.jit.unused
     def _restore_output_dtype(self, h: Tensor, input: Tensor) -> Tensor:

@@ -67,6 +67,42 @@ def test_regression_artifact_host_code_on_cpu(regression_case, host_on_cpu):
     assert (c - rc["c"]).abs().max() <= 1e-6
 
 
+def test_dropout_masks_of_all_layers_come_from_one_draw(host_on_cpu, monkeypatch):
+    """In training an ``SRU`` draws the masks of all its layers at once (the reference draws one per layer,
+    sru/modules.py:380-387); a layer whose ``get_dropout_mask_`` was replaced keeps drawing its own, and every
+    mask is used exactly once, with values 0 or 1/(1-p)."""
+    modules = host_on_cpu
+    torch.manual_seed(3)
+    model = modules.SRU(6, 8, num_layers=4, dropout=0.25, bidirectional=True).train()
+    calls, seen = [], []
+    orig = modules.SRUCell.get_dropout_mask_
+    monkeypatch.setattr(modules.SRUCell, "get_dropout_mask_", lambda self, size, p: (calls.append(size), orig(self, size, p))[1])
+    rec = modules.ops.elementwise_recurrence_gpu
+
+    def spy(U, x, V, bias, c0, act, d, bi, skip, scale=None, mask_c=None, *args, **kw):
+        seen.append(mask_c)
+        return rec(U, x, V, bias, c0, act, d, bi, skip, scale, mask_c, *args, **kw)
+    monkeypatch.setattr(modules.ops, "elementwise_recurrence_gpu", spy)
+    x = torch.randn(5, 3, 6)
+    h, c = model(x)
+    assert torch.isfinite(h).all() and not calls                 # no per-layer draw
+    assert [m is not None for m in seen] == [True, True, True, False]      # no dropout after the last layer
+    assert len({m.data_ptr() for m in seen[:3]}) == 3            # three different slices
+    for m in seen[:3]:
+        assert m.shape == (3, 16) and m.is_contiguous()
+        assert all(v == 0.0 or abs(v - 1.0 / 0.75) < 1e-6 for v in m.unique().tolist())
+    assert all(cell.__dict__.get("_preset_mask_c") is None for cell in model.rnn_lst)
+    # a replaced mask function on one layer: that layer draws for itself, the others still share one draw
+    del calls[:], seen[:]
+    model.rnn_lst[1].get_dropout_mask_ = lambda size, p: torch.ones(size)
+    model(x)
+    assert not calls and torch.equal(seen[1], torch.ones(3, 16))
+    model.eval()
+    del seen[:]
+    model(x)
+    assert all(m is None for m in seen)
+
+
 def test_cell_geometry():
     cell = SRUCell(6, 8, bidirectional=True, n_proj=4)
     assert cell.num_matrices == 4 and cell.projection_size == 4
