@@ -75,6 +75,8 @@ int sru_b200_check_device_error(void *stream);
  *   gemm_ksplit, gemm_2sm, gemm_epi_warps    K slabs, pair kernel on/off, epilogue warps (4 or 8)
  *   gemm_raster                        tile order of the persistent GEMM grid: 1 consecutive tiles run down M,
  *                                      0 along N (default: whichever re-reads the smaller operand)
+ *   gemm_tma_store                     16-bit output of the pair GEMM through tiled bulk stores from shared memory
+ *                                      (1) or warp stores (0); default: bulk stores for K <= 512
  *   gemm_dynamic                       1: the pair GEMM hands out its tiles dynamically (needs the
  *                                      workspace form of the call); for products that share the GPU with
  *                                      a collective

@@ -25,7 +25,7 @@ int set_error(int code, const char *fmt, ...) {
 // ---- options: environment defaults read once, then changed only through sru_b200_set_option ----
 static const char *const kOptionNames[OPT_COUNT] = {
     "fwd_v", "bwd_v", "scan_threads", "fwd_threads", "bwd_threads", "scan_ss", "scan_stages",
-    "force_generic", "fwd_split", "gemm_ksplit", "gemm_2sm", "gemm_epi_warps", "gemm_dynamic", "gemm_raster"};
+    "force_generic", "fwd_split", "gemm_ksplit", "gemm_2sm", "gemm_epi_warps", "gemm_dynamic", "gemm_raster", "gemm_tma_store"};
 static std::atomic<int> g_options[OPT_COUNT];
 static std::once_flag g_options_once;
 

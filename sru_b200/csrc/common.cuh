@@ -25,7 +25,7 @@ int ensure_context();      // binds the device's primary context to this thread 
 enum Option {
     OPT_FWD_V, OPT_BWD_V, OPT_SCAN_THREADS, OPT_FWD_THREADS, OPT_BWD_THREADS, OPT_SCAN_SS, OPT_SCAN_STAGES,
     OPT_FORCE_GENERIC, OPT_FWD_SPLIT, OPT_GEMM_KSPLIT, OPT_GEMM_2SM, OPT_GEMM_EPI_WARPS, OPT_GEMM_DYNAMIC,
-    OPT_GEMM_RASTER, OPT_COUNT
+    OPT_GEMM_RASTER, OPT_GEMM_TMA_STORE, OPT_COUNT
 };
 int option(Option o, int dflt);   // the option's value, or dflt when it is not set
 

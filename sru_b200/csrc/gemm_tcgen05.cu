@@ -65,6 +65,7 @@ struct GemmArgs {
     // NULL: static order (unit = pair, pair + pairs, ...).
     unsigned long long *sched;
     int epi_warps;      // pair kernel instance: 8 or 4 epilogue warps per CTA (host side only)
+    int c_tma;          // pair kernel: 16-bit output leaves shared memory through tiled bulk stores (map_c is valid)
     int *err;
 };
 
@@ -175,6 +176,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
         : "memory");
 }
+// Tiled bulk store: a box of this CTA's shared memory (128-byte swizzled, as the map says) to global memory; rows and
+// columns of the box that lie outside the tensor are not written.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(ncols)
                  : "memory");
@@ -211,6 +221,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// The same wait, naming the registers an earlier tcgen05.ld fills: their readers cannot be scheduled above it.
+__device__ __forceinline__ void tmem_ld_wait_for(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                   "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                   "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :
+                 : "memory");
+}
 
 // Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
 __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
@@ -440,8 +460,9 @@ constexpr int kBStage2 = 128 * BK * 2;   // 16 KB: this CTA's 128 columns of B
 constexpr int kEpiWarps2 = 8;
 constexpr int kThreads2 = 64 + 32 * kEpiWarps2;
 constexpr int kStgRow = 128 * 2;               // staged output row: 128 16-bit columns, 16-byte chunks XOR-swizzled by row
-constexpr int kStgWarp = 32 * kStgRow;         // per epilogue warp
-constexpr int kSmemBytes2 = kStages2 * (kAStage2 + kBStage2) + 1024 + 256 + kEpiWarps2 * kStgWarp;
+constexpr int kStgWarp = 32 * kStgRow;         // per epilogue warp; 1024-byte aligned (two 32 x 128-byte store boxes)
+constexpr int kBarBytes2 = 1024;               // barriers + the tensor-memory slot, padded to the staging alignment
+constexpr int kSmemBytes2 = kStages2 * (kAStage2 + kBStage2) + 1024 + kBarBytes2 + kEpiWarps2 * kStgWarp;
 static_assert(kSmemBytes2 <= 227 * 1024, "pair kernel shared memory");
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -498,29 +519,30 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t adesc, uin
 // that is 32 different 128-byte lines per store instruction.  Instead the converted values go to a
 // per-warp buffer row by row and are read back so that half a warp covers 256 contiguous bytes of
 // one output row: every store instruction then writes two full 256-byte row segments.
-template <typename TO>
+//
+// With a tensor map of C (map_c != nullptr) the second half goes away: the buffer is laid out as two boxes of 32 rows x
+// 128 bytes in the 128-byte swizzle of the map (chunk j of row r at chunk j ^ (r & 7): conflict-free for the row-wise
+// writes as well) and one lane hands both boxes to the TMA engine, which also clips rows beyond M and columns beyond N.
+// The warp goes straight back to the accumulator; before it writes the buffer again it waits until the engine has read it.
+template <typename TO, bool AHEAD>
 __device__ __forceinline__ void epilogue_staged(const GemmArgs &g, uint32_t tmem_warp, int64_t row0, int64_t col_base,
-                                                uint8_t *stg, int lane, int h) {
+                                                uint8_t *stg, int lane, int h, const CUtensorMap *map_c) {
     const int64_t row = row0 + lane;
     {
         const int64_t colh = col_base + h * 128;
         if (colh >= g.N) return;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-            const int64_t col0 = colh + c * 32;
-            if (col0 >= g.N) break;
-            // the chunk's 32 bias values are requested BEFORE the accumulator load and its wait, so that their latency
-            // hides behind it (all lanes read the same addresses: one broadcast transaction per request)
-            float4 bv[8];
+        // the chunk's 32 bias values are requested BEFORE the wait for the accumulator load, so that their latency
+        // hides behind it (all lanes read the same addresses: one broadcast transaction per request)
+        auto load_bias = [&](int64_t col0, float4 (&bv)[8]) {
             if (g.bias) {
 #pragma unroll
                 for (int q4 = 0; q4 < 8; ++q4)
                     bv[q4] = (col0 + q4 * 4 < g.N) ? __ldg(reinterpret_cast<const float4 *>(g.bias + col0) + q4)
                                                    : make_float4(0.f, 0.f, 0.f, 0.f);
             }
-            uint32_t r[32];
-            tmem_ld32(tmem_warp + h * 128 + c * 32, r);
-            tmem_ld_wait();
+        };
+        // one chunk of 32 accumulator columns: bias, accumulate, convert, stage
+        auto stage_chunk = [&](int c, int64_t col0, const uint32_t (&r)[32], const float4 (&bv)[8]) {
 #pragma unroll
             for (int j0 = 0; j0 < 32; j0 += 8) {
                 float v[8];
@@ -538,10 +560,60 @@ __device__ __forceinline__ void epilogue_staged(const GemmArgs &g, uint32_t tmem
                         for (int j = 0; j < 8; ++j) v[j] += Cvt<TO>::to_f(crow[j]);
                     }
                 }
-                // 16-byte chunk (c*4 + j0/8) of this lane's row, XOR-swizzled so that the eight lanes of a
-                // shared-memory phase hit eight different bank groups
-                store8<TO>(reinterpret_cast<TO *>(stg + lane * kStgRow + (((c * 4 + (j0 >> 3)) ^ (lane & 15)) << 4)), v);
+                const int chunk = c * 4 + (j0 >> 3);      // 16-byte chunk of this lane's 256-byte row
+                if (map_c)
+                    store8<TO>(reinterpret_cast<TO *>(stg + (chunk >> 3) * 4096 + lane * 128 + (((chunk & 7) ^ (lane & 7)) << 4)), v);
+                else
+                    store8<TO>(reinterpret_cast<TO *>(stg + lane * kStgRow + ((chunk ^ (lane & 15)) << 4)), v);
             }
+        };
+        if constexpr (AHEAD) {
+            // The accumulator chunks are requested one ahead: chunk c + 1 travels from tensor memory while chunk c is
+            // converted and staged (two register sets; the loop is unrolled so that their indices are constants).
+            // For the instance with four epilogue warps (long reductions: 5 % on the 256 000 x 6144 x 2048 product);
+            // the eight-warp instance has 200 registers per thread and spills with two sets (measured: 30 % slower).
+            uint32_t r[2][32];
+            tmem_ld32(tmem_warp + h * 128, r[0]);
+            if (map_c) {
+                if (lane == 0) bulk_wait_read_all();
+                __syncwarp();
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int64_t col0 = colh + c * 32;
+                if (col0 >= g.N) break;
+                float4 bv[8];
+                load_bias(col0, bv);
+                tmem_ld_wait_for(r[c & 1]);
+                if (c < 3 && col0 + 32 < g.N) tmem_ld32(tmem_warp + h * 128 + (c + 1) * 32, r[(c + 1) & 1]);
+                stage_chunk(c, col0, r[c & 1], bv);
+            }
+        } else {
+            if (map_c) {
+                if (lane == 0) bulk_wait_read_all();
+                __syncwarp();
+            }
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                const int64_t col0 = colh + c * 32;
+                if (col0 >= g.N) break;
+                float4 bv[8];
+                load_bias(col0, bv);
+                uint32_t r[32];
+                tmem_ld32(tmem_warp + h * 128 + c * 32, r);
+                tmem_ld_wait();
+                stage_chunk(c, col0, r, bv);
+            }
+        }
+        if (map_c) {
+            fence_proxy_async();      // the generic-proxy writes above become visible to the bulk copy engine
+            __syncwarp();
+            if (lane == 0 && row0 < g.M) {
+                tma_store_2d(map_c, smem_u32(stg), (int)colh, (int)row0);
+                if (colh + 64 < g.N) tma_store_2d(map_c, smem_u32(stg) + 4096, (int)colh + 64, (int)row0);
+                bulk_commit();
+            }
+            return;
         }
         __syncwarp();
         const int sub = lane >> 4, seg = lane & 15;          // two rows per pass, 16 x 16 bytes per row
@@ -561,7 +633,7 @@ __device__ __forceinline__ void epilogue_staged(const GemmArgs &g, uint32_t tmem
 template <int EW>     // working epilogue warps per CTA: 4 (192 threads) or 8 (320 threads)
 __global__ void __launch_bounds__(64 + 32 * EW, 1)
 gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                        const GemmArgs g) {
+                        const __grid_constant__ CUtensorMap map_c, const GemmArgs g) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *smem_a = smem;
@@ -703,7 +775,7 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
         const int h_first = (EW == 8) ? ((warp - 2) >> 2) : 0;   // 128-column halves this warp converts
         const int h_last = (EW == 8) ? h_first : 1;
         const uint32_t tempty_leader = map_to_cta(bar_tempty, 0);
-        uint8_t *stg = smem + kStages2 * (kAStage2 + kBStage2) + 256 + (warp - 2) * kStgWarp;
+        uint8_t *stg = smem + kStages2 * (kAStage2 + kBStage2) + kBarBytes2 + (warp - 2) * kStgWarp;
         bool ok = true;
         UnitReader reader;
         reader.init(g, pair);
@@ -726,10 +798,10 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             const uint32_t tmem_warp = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
             if (g.c_dtype == SRU_BF16) {
                 for (int h = h_first; h <= h_last; ++h)
-                    epilogue_staged<__nv_bfloat16>(g, tmem_warp, row0, col_base, stg, lane, h);
+                    epilogue_staged<__nv_bfloat16, EW == 4>(g, tmem_warp, row0, col_base, stg, lane, h, g.c_tma ? &map_c : nullptr);
             } else if (g.c_dtype == SRU_F16) {
                 for (int h = h_first; h <= h_last; ++h)
-                    epilogue_staged<__half>(g, tmem_warp, row0, col_base, stg, lane, h);
+                    epilogue_staged<__half, EW == 4>(g, tmem_warp, row0, col_base, stg, lane, h, g.c_tma ? &map_c : nullptr);
             } else {
 #pragma unroll 1
                 for (int c = h_first * 4; c < h_last * 4 + 4; ++c) {
@@ -745,6 +817,7 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(tempty_leader + 8 * acc);
         }
+        if (g.c_tma && lane == 0) bulk_wait_all();     // this warp's stores have left shared memory and are complete
     }
 
     // -------------------------------- teardown --------------------------------
@@ -983,6 +1056,20 @@ static int gemm_impl(void *c, const void *a, const void *b, const float *col_bia
         attr_set[dev] = true;
     }
     g.sched = nullptr;
+    // 16-bit output of the pair kernel leaves through tiled bulk stores where the epilogue sets the pace of a tile
+    // (K <= 512).  Measured on B200, bulk stores against warp stores: 256 000 x 8192 x 120  1544 -> 1310 us,
+    // 16 384 x 6144 x 512  101.9 -> 96.0, 16 384 x 4096 x 512  74.0 -> 68.7; level at K = 1024; with long reductions,
+    // where four epilogue warps do both halves of a tile through one buffer and the loads keep the copy engine
+    // busy, they LOSE (256 000 x 6144 x 2048  4745 -> 4973 us, 256 000 x 2048 x 6144  4413 -> 5220).
+    // Option gemm_tma_store forces either way.
+    CUtensorMap map_c;
+    memset(&map_c, 0, sizeof(map_c));
+    g.c_tma = 0;
+    if (two_sm && g.c_dtype != SRU_F32 && option(OPT_GEMM_TMA_STORE, nkb_all <= 8 ? 1 : 0)) {
+        rc = make_map(&map_c, g.c, g.c_dtype, n, m, g.ldc, 64, 32);
+        if (rc) return rc;
+        g.c_tma = 1;
+    }
     g.epi_warps = (nkb_all <= 16) ? 8 : 4;      // see the epilogue of the pair kernel
     const int epi_forced = option(OPT_GEMM_EPI_WARPS, -1);
     if (epi_forced >= 0) g.epi_warps = (epi_forced == 8) ? 8 : 4;
@@ -1008,8 +1095,8 @@ static int gemm_impl(void *c, const void *a, const void *b, const float *col_bia
         attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        if (g.epi_warps == 8) SRUB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tcgen05_2sm_kernel<8>, map_a, map_b, g));
-        else SRUB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tcgen05_2sm_kernel<4>, map_a, map_b, g));
+        if (g.epi_warps == 8) SRUB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tcgen05_2sm_kernel<8>, map_a, map_b, map_c, g));
+        else SRUB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tcgen05_2sm_kernel<4>, map_a, map_b, map_c, g));
     } else {
         const unsigned grid = (unsigned)std::min<int64_t>(ntiles, plan.workers);
         gemm_tcgen05_kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(map_a, map_b, g);

@@ -136,6 +136,44 @@ def test_gemm_split_k(force):
     assert rel_err(out, ref) <= 1e-4 and rel_err(out16, ref) <= 1e-2 and rel_err(acc, ref + base) <= 1e-4
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("size", [
+    # M,    N,    K       ragged rows / a second store box partly or wholly outside N / eight and four epilogue warps
+    (1000, 6144, 2048), (4096, 3072, 1024), (777, 264, 120), (2500, 200, 64), (300, 520, 1280), (256 * 9, 256 * 5 + 72, 512)])
+def test_gemm_tma_store_epilogue(size, dtype):
+    """16-bit output of the pair kernel through tiled bulk stores from shared memory (default) against the same
+    kernel writing with warp stores: bit-identical, with a column bias, when accumulating onto C, and into a strided
+    output whose guard columns and rows stay untouched."""
+    from sru_b200 import _lib
+    gemm = _gemm()
+    M, N, K = size
+    g = torch.Generator().manual_seed(M * 3 + N + K)
+    a = (torch.randn(M, K, generator=g) * 0.5).to(dtype).to(DEV)
+    b = (torch.randn(K, N, generator=g) * 0.5).to(dtype).to(DEV)
+    bias = torch.randn(N, generator=g).to(DEV)
+    base = torch.randn(M, N, generator=g).to(dtype).to(DEV)
+    got = {}
+    for tma in (0, 1):
+        with _lib.options(gemm_2sm=1, gemm_tma_store=tma):
+            plain = gemm(a, b)
+            biased = gemm(a, b, col_bias=bias)
+            acc = base.clone()
+            gemm(a, b, out=acc, accumulate=True)
+            big = torch.full((M + 3, N + 24), 7.0, dtype=dtype, device=DEV)
+            gemm(a, b, out=big[:M, 8:8 + N])
+            got[tma] = (plain, biased, acc, big)
+    torch.cuda.synchronize()
+    _lib.check_device_error()
+    ref = a.float() @ b.float()
+    tol = 1e-2 if dtype == torch.bfloat16 else 2e-3
+    assert rel_err(got[1][0], ref) <= tol and rel_err(got[1][1], ref + bias) <= tol
+    assert rel_err(got[1][2], ref + base.float()) <= tol
+    for x, y in zip(got[0], got[1]):
+        assert torch.equal(x, y)
+    big = got[1][3]
+    assert torch.all(big[M:] == 7.0) and torch.all(big[:, :8] == 7.0) and torch.all(big[:, 8 + N:] == 7.0)
+
+
 @pytest.mark.parametrize("layout", ["nn", "nt", "tn"])
 @pytest.mark.parametrize("size", [(4096, 3072, 1024), (256 * 37, 256 * 9, 320), (2048, 6144, 64), (1000, 6144, 2048)])
 def test_gemm_dynamic_tile_order(size, layout):
