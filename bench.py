@@ -317,6 +317,9 @@ def main():
                     help="leave the gate bias to the scan instead of the GEMM epilogue (A/B measurement)")
     ap.add_argument("--sustain-seconds", type=float, default=3.0,
                     help="N > 1: after the timed steps, keep stepping for about this long and report that step time too")
+    ap.add_argument("--c-hist", default="float32", choices=["float32", "storage"],
+                    help="type of the saved state history: float32 (default) or the 16-bit storage type (2 bytes less "
+                         "per column-step in both scans, at the accuracy cost described in DESIGN.md)")
     ap.add_argument("--batch", type=int, default=0,
                     help="override the global batch (profiling on a small case; the workload name says so)")
     ap.add_argument("--length", type=int, default=0,
@@ -367,6 +370,7 @@ def main():
     if args.no_bias_fold:
         from sru_b200 import projection
         projection.set_bias_fold_enabled(False)
+    ops.set_c_hist_dtype(args.c_hist)
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
