@@ -485,6 +485,9 @@ def main():
     # ---- what the step computed: the loss and a checksum of one layer's (reduced) weight gradient ----
     check = None
     if cfg["train"]:
+        # the check step always uses the first draw of the global dropout masks, whatever --steps / --warmup were, so
+        # that its numbers compare across runs and world sizes
+        use_global_dropout_masks(model, cfg["B"], rank, world, seed=1234)
         out_loss = run_step(model, cfg, x_dev, mask_dev, c0, tokens_global, reducer)
         loss_t = out_loss.double().clone()
         if world > 1:
