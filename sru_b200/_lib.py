@@ -161,12 +161,31 @@ class KernelTimer:
 
 timer = None          # a KernelTimer, or None
 launch_count = 0      # kernels of this library launched so far (bench.py reports the per-step figure)
+nvtx_ranges = os.environ.get("SRU_B200_NVTX", "0") not in ("", "0")   # see set_nvtx_ranges
+
+
+def set_nvtx_ranges(enabled: bool) -> None:
+    """Brackets every C-ABI launch with an NVTX range named after its kernel class ("scan_fwd", "gemm_wgrad", ...),
+    so that a profiler can filter or group by it (for instance ``ncu --nvtx --nvtx-include "scan_bwd/"``).
+    Off by default; also switched on by the environment variable SRU_B200_NVTX=1."""
+    global nvtx_ranges
+    nvtx_ranges = bool(enabled)
 
 
 def call(name, n_kernels, fn, *args):
     """Invoke a C-ABI entry point, count its kernel launches, time it if a timer is installed."""
     global launch_count
     launch_count += n_kernels
+    if nvtx_ranges:
+        torch.cuda.nvtx.range_push(name)
+        try:
+            return _call(name, fn, *args)
+        finally:
+            torch.cuda.nvtx.range_pop()
+    return _call(name, fn, *args)
+
+
+def _call(name, fn, *args):
     if timer is None:
         return check(fn(*args))
     start = torch.cuda.Event(enable_timing=True)

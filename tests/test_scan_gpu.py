@@ -476,3 +476,17 @@ def test_split_role_forward(shape, v, dtype):
             assert torch.equal(a[1], b[1])
     torch.cuda.synchronize()
     _lib.check_device_error()
+
+
+def test_nvtx_ranges():
+    """NVTX ranges around the library's launches (for profiler filters) change nothing else."""
+    from sru_b200 import _lib
+    inp = random_inputs(33, 5, 64, 2, 3, pad="tail", scale=1.0, seed=91)
+    out0, ref = run_both(inp, torch.bfloat16)
+    _lib.set_nvtx_ranges(True)
+    try:
+        out1, _ = run_both(inp, torch.bfloat16)
+    finally:
+        _lib.set_nvtx_ranges(False)
+    for k in out0:
+        assert torch.equal(out0[k], out1[k]), k
