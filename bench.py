@@ -319,7 +319,7 @@ def main():
                     help="N > 1: after the timed steps, keep stepping for about this long and report that step time too")
     ap.add_argument("--c-hist", default="float32", choices=["float32", "storage"],
                     help="type of the saved state history: float32 (default) or the 16-bit storage type (2 bytes less "
-                         "per column-step in both scans, at the accuracy cost described in DESIGN.md)")
+                         "per column-step in both scans; backward then feeds a 16-bit-rounded c[t-1] into the sigmoid)")
     ap.add_argument("--batch", type=int, default=0,
                     help="override the global batch (profiling on a small case; the workload name says so)")
     ap.add_argument("--length", type=int, default=0,
