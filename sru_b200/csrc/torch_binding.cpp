@@ -234,9 +234,81 @@ Tensor b200_layer_norm(const Tensor &x, const OptTensor &weight, const OptTensor
     return y;
 }
 
+// The layer loop of an inference forward as ONE call (sru/modules.py:617-646 is a Python loop over the layers, each
+// of them a matrix product and a recurrence launch): per layer the gate bias is laid out for the product's epilogue,
+// U = x W (+ bias) runs on the tcgen05 GEMM, and the scan reads U (and x as the highway input when k = 3) and writes
+// h in the storage type and the layer's final state in float32.  For stacks of plain layers (no layer norm, no
+// factorised projection, no custom module, identity activation) on 16-bit inputs whose shapes the GEMM takes
+// (rows, input width and D*k multiples of 8); the Python module checks that and otherwise keeps its own loop.
+// Same kernels with the same arguments as that loop: identical results.
+std::vector<Tensor> b200_stack_forward(const Tensor &x, std::vector<Tensor> weights, std::vector<Tensor> weight_c,
+                                       std::vector<Tensor> bias, std::vector<double> scale_x, const OptTensor &c0,
+                                       const OptTensor &mask_pad, int64_t hidden, bool bidirectional,
+                                       std::vector<int64_t> ks, std::vector<int64_t> skips) {
+    TORCH_CHECK(x.is_cuda() && x.dim() == 3, "sru_b200::stack_forward: x must be a CUDA tensor (length, batch, width)");
+    const auto st = x.scalar_type();
+    TORCH_CHECK(st == at::kHalf || st == at::kBFloat16, "sru_b200::stack_forward: 16-bit input expected");
+    const size_t n = weights.size();
+    TORCH_CHECK(n > 0 && weight_c.size() == n && bias.size() == n && scale_x.size() == n && ks.size() == n &&
+                skips.size() == n, "sru_b200::stack_forward: one entry per layer expected in every list");
+    c10::cuda::CUDAGuard guard(x.device());
+    void *stream = at::cuda::getCurrentCUDAStream().stream();
+    const int dirs = bidirectional ? 2 : 1;
+    const int64_t L = x.size(0), B = x.size(1), D = hidden * dirs, M = L * B;
+    TORCH_CHECK(M > 0 && M % 8 == 0, "sru_b200::stack_forward: length * batch must be a positive multiple of 8");
+    const int code = dtype_code(st);
+    const auto f32 = x.options().dtype(at::kFloat);
+    Tensor pad;
+    if (mask_pad.has_value()) {
+        pad = mask_pad.value().to(at::kBool).contiguous();
+        TORCH_CHECK(pad.dim() == 2 && pad.size(0) == L && pad.size(1) == B, "sru_b200::stack_forward: mask_pad must be (length, batch)");
+    }
+    Tensor init;
+    if (c0.has_value()) {
+        init = c0.value().to(at::kFloat).contiguous();
+        TORCH_CHECK(init.dim() == 3 && init.size(0) == (int64_t)n && init.size(1) == B && init.size(2) == D,
+                    "sru_b200::stack_forward: c0 must be (layers, batch, width)");
+    }
+    Tensor c_stack = at::empty({(int64_t)n, B, D}, f32);
+    Tensor cur = x.contiguous();
+    for (size_t i = 0; i < n; ++i) {
+        const int64_t in = cur.size(2), k = ks[i], N = D * k, skip = skips[i];
+        TORCH_CHECK(weights[i].dim() == 2 && weights[i].size(0) == in && weights[i].size(1) == N,
+                    "sru_b200::stack_forward: weight of layer ", i, " must be (", in, ", ", N, ")");
+        TORCH_CHECK(in % 8 == 0 && N % 8 == 0, "sru_b200::stack_forward: widths must be multiples of 8");
+        TORCH_CHECK((k == 3 || k == 4) && (skip == 0 || (skip == 1 && k == 3 && in == D) || (skip == 2 && k == 4)),
+                    "sru_b200::stack_forward: layer ", i, " has k = ", k, " with skip type ", skip);
+        Tensor w = weights[i].to(st).contiguous();
+        Tensor wc = weight_c[i].to(at::kFloat).contiguous();
+        Tensor b = bias[i].to(at::kFloat).contiguous();
+        TORCH_CHECK(wc.numel() == 2 * D && b.numel() == 2 * D, "sru_b200::stack_forward: weight_c and bias hold 2 * width values");
+        Tensor col_bias = at::empty({N}, f32);
+        int rc = sru_b200_gate_bias_columns(col_bias.data_ptr<float>(), b.data_ptr<float>(), D, (int)k, stream);
+        TORCH_CHECK(rc == 0, "sru_b200::stack_forward: ", sru_b200_last_error());
+        Tensor u = at::empty({M, N}, cur.options());
+        const size_t wbytes = sru_b200_gemm_workspace_bytes(M, N, in, 1);
+        Tensor ws = at::empty({(int64_t)std::max<size_t>(wbytes, 16)}, x.options().dtype(at::kByte));
+        rc = sru_b200_gemm_ws(u.data_ptr(), cur.data_ptr(), w.data_ptr(), col_bias.data_ptr<float>(), M, N, in, in, N, N,
+                              0, 0, code, code, 0, ws.data_ptr(), wbytes, stream);
+        TORCH_CHECK(rc == 0, "sru_b200::stack_forward: ", sru_b200_last_error());
+        Tensor h = at::empty({L, B, D}, cur.options());
+        rc = sru_b200_scan_forward(h.data_ptr(), nullptr, c_stack[i].data_ptr(), u.data_ptr(),
+                                   skip == 1 ? cur.data_ptr() : nullptr, wc.data_ptr(), nullptr,
+                                   init.defined() ? init[i].data_ptr() : nullptr, nullptr,
+                                   static_cast<const uint8_t *>(ptr(pad)), L, B, hidden, dirs, (int)k, 0, (int)skip, 0,
+                                   scale_x[i], code, SRU_F32, stream);
+        TORCH_CHECK(rc == 0, "sru_b200::stack_forward: ", sru_b200_last_error());
+        cur = h;
+    }
+    return {cur, c_stack};
+}
+
 }  // namespace
 
 TORCH_LIBRARY(sru_b200, m) {
+    m.def("stack_forward(Tensor x, Tensor[] weights, Tensor[] weight_c, Tensor[] bias, float[] scale_x, Tensor? c0, "
+          "Tensor? mask_pad, int hidden_size, bool bidirectional, int[] k, int[] skip_type) -> Tensor[]",
+          &b200_stack_forward);
     m.def("gemm(Tensor x, Tensor w, Tensor? col_bias) -> Tensor", &b200_gemm);
     m.def("gate_bias_columns(Tensor bias, int width, int k) -> Tensor", &b200_gate_bias_columns);
     m.def("layer_norm(Tensor x, Tensor? weight, Tensor? bias, float eps) -> Tensor", &b200_layer_norm);

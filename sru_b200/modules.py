@@ -34,6 +34,14 @@ def _load_scripted_ops() -> bool:
 
 
 _HAVE_TORCH_OPS = _load_scripted_ops()
+_native_stack_enabled = True
+
+
+def set_native_stack_enabled(enabled: bool) -> None:
+    """Whether an inference ``SRU.forward`` of plain layers runs its layer loop as one native call
+    (``sru_b200::stack_forward``; default) or as the Python loop over ``SRUCell.forward_native``."""
+    global _native_stack_enabled
+    _native_stack_enabled = bool(enabled)
 
 if _HAVE_TORCH_OPS:
 
@@ -498,19 +506,25 @@ class SRU(nn.Module):
             c0_ = [x.squeeze(0) for x in c0.chunk(self.num_layers, 0)]
 
         prevx = input if self.input_to_hidden is None else self.input_to_hidden(input)
+        native: Optional[List[Tensor]] = None
         if not torch.jit.is_scripting():
-            self._preset_dropout_masks(input.size(1))
-        lstc = []
-        i = 0
-        for rnn in self.rnn_lst:
-            h, c = rnn.forward_native(prevx, c0_[i], mask_pad=mask_pad)
-            prevx = h
-            lstc.append(c)
-            i += 1
+            native = self._forward_native_stack(prevx, c0, mask_pad)
+        if native is not None:
+            prevx, lstc_stack = native[0], native[1]
+        else:
+            if not torch.jit.is_scripting():
+                self._preset_dropout_masks(input.size(1))
+            lstc = []
+            i = 0
+            for rnn in self.rnn_lst:
+                h, c = rnn.forward_native(prevx, c0_[i], mask_pad=mask_pad)
+                prevx = h
+                lstc.append(c)
+                i += 1
+            lstc_stack = torch.stack(lstc)
         if not torch.jit.is_scripting():
             prevx = self._restore_output_dtype(prevx, input)
 
-        lstc_stack = torch.stack(lstc)
         if self.nn_rnn_compatible_return:
             batch_size = input.size(1)
             lstc_stack = lstc_stack.view(self.num_layers, batch_size, self.num_directions, self.hidden_size)
@@ -520,6 +534,49 @@ class SRU(nn.Module):
         if isinstance(orig_input, PackedSequence):
             prevx = nn.utils.rnn.pack_padded_sequence(prevx, lengths, enforce_sorted=False)
         return prevx, lstc_stack
+
+    @torch.jit.unused
+    def _forward_native_stack(self, x: Tensor, c0: Optional[Tensor], mask_pad: Optional[Tensor]) -> Optional[List[Tensor]]:
+        """Inference through ``sru_b200::stack_forward``: the whole layer loop as one native call (one Python to
+        C++ transition instead of several per layer; same kernels and arguments as the loop, identical results).
+        Returns None when the stack or the call is not of the plain kind that operator serves: gradients needed,
+        training mode, layer norm, factorised or custom projections, a non-identity activation, fp32 compute,
+        widths the tensor-core GEMM does not take, the per-kernel timer of the benchmark installed."""
+        if (not _HAVE_TORCH_OPS or not _native_stack_enabled or torch.is_grad_enabled() or self.training
+                or not x.is_cuda or x.dim() != 3 or _lib.timer is not None or ops.get_amp_mode() != "native"
+                or gemm_backend() != "tcgen05" or not bias_fold_enabled()):
+            return None
+        length, batch = x.size(0), x.size(1)
+        if length == 0 or (length * batch) % 8 != 0:
+            return None
+        first = self.rnn_lst[0]
+        dt = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else (
+            first.weight.dtype if first.weight.dtype != x.dtype else x.dtype)
+        if dt not in (torch.float16, torch.bfloat16):
+            return None
+        D = self.output_size
+        width = x.size(2)
+        ks: List[int] = []
+        skips: List[int] = []
+        scales: List[float] = []
+        for cell in self.rnn_lst:
+            k = cell.num_matrices
+            if (cell.layer_norm is not None or cell.weight_proj is not None or cell.custom_m is not None
+                    or cell.activation_type != 0 or cell.amp_recurrence_fp16 or cell.output_size != D
+                    or cell.weight.size(0) != width or width % 8 != 0 or (D * k) % 8 != 0
+                    or cell.weight.dtype not in (torch.float32, dt) or not cell.weight.is_cuda):
+                return None
+            ks.append(k)
+            skips.append(0 if not cell.has_skip_term else (1 if k == 3 else 2))
+            scales.append(ops._scale_value(cell.scale_x if cell.rescale else None))
+            width = D
+        if c0 is not None and (c0.dim() != 3 or c0.size(0) != self.num_layers):
+            return None
+        out = torch.ops.sru_b200.stack_forward(
+            x if x.dtype == dt else x.to(dt), [c.weight for c in self.rnn_lst], [c.weight_c for c in self.rnn_lst],
+            [c.bias for c in self.rnn_lst], scales, c0, mask_pad, self.hidden_size, self.bidirectional, ks, skips)
+        _lib.launch_count += 3 * len(ks)      # per layer: bias layout, product, scan
+        return [out[0], out[1]]
 
     @torch.jit.unused
     def _preset_dropout_masks(self, batch_size: int) -> None:

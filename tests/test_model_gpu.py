@@ -333,3 +333,57 @@ def test_scale_x_changes_take_effect():
     cell.reset_parameters()
     cpu = to_oracle(model).eval()
     assert agree()
+
+
+@pytest.mark.parametrize("kwargs,L,B,in_size,use_mask,use_c0", [
+    (dict(hidden_size=64, num_layers=3), 24, 8, 64, False, False),                         # k = 3 everywhere
+    (dict(hidden_size=64, num_layers=3, bidirectional=True), 31, 8, 40, True, True),       # k = 4 first layer, padding
+    (dict(hidden_size=128, num_layers=2, highway_bias=-2.0, rescale=True), 16, 4, 128, True, False),
+    (dict(hidden_size=32, num_layers=2, has_skip_term=False), 8, 8, 32, False, True),
+])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_native_layer_loop_matches_python_loop(kwargs, L, B, in_size, use_mask, use_c0, dtype):
+    """Inference through ``sru_b200::stack_forward`` (the layer loop as one native call) gives the bits of the
+    Python loop over the layers: same kernels, same arguments.  Under autocast on fp32 input and on 16-bit input
+    with 16-bit weights; stacks it does not serve (layer norm, training mode) keep the Python loop."""
+    from sru_b200 import _lib, modules
+    SRU = _sru()
+    torch.manual_seed(L + B)
+    model = SRU(in_size, **kwargs).to(DEV).eval()
+    D = model.output_size
+    x = torch.randn(L, B, in_size, device=DEV)
+    mask = None
+    if use_mask:
+        lens = torch.randint(L // 2, L + 1, (B,))
+        mask = (torch.arange(L).view(L, 1) >= lens.view(1, B)).to(DEV)
+    c0 = torch.randn(model.num_layers, B, D, device=DEV) * 0.3 if use_c0 else None
+
+    def run(native, autocast):
+        modules.set_native_stack_enabled(native)
+        try:
+            n0 = _lib.launch_count
+            with torch.no_grad():
+                if autocast:
+                    with torch.autocast("cuda", dtype=dtype):
+                        h, c = model(x, c0, mask_pad=mask)
+                else:
+                    m16 = SRU(in_size, **kwargs).to(DEV).eval()
+                    m16.load_state_dict(model.state_dict())
+                    m16 = m16.to(dtype)
+                    h, c = m16(x.to(dtype), None if c0 is None else c0.to(dtype), mask_pad=mask)
+            return h, c, _lib.launch_count - n0
+        finally:
+            modules.set_native_stack_enabled(True)
+    for autocast in (True, False):
+        h1, c1, n1 = run(True, autocast)
+        h0, c0_, n0 = run(False, autocast)
+        torch.cuda.synchronize()
+        _lib.check_device_error()
+        assert h1.dtype == h0.dtype and c1.dtype == c0_.dtype and h1.shape == h0.shape and c1.shape == c0_.shape
+        assert torch.equal(h1, h0) and torch.equal(c1, c0_)
+        assert n1 == n0 == 3 * model.num_layers          # bias layout, product, scan per layer on both paths
+    # not served: falls back to the Python loop and still works
+    ln = SRU(in_size, layer_norm=True, **kwargs).to(DEV).eval()
+    with torch.no_grad(), torch.autocast("cuda", dtype=dtype):
+        h, c = ln(x, mask_pad=mask)
+    assert torch.isfinite(h).all()
