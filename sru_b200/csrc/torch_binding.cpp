@@ -235,22 +235,44 @@ Tensor b200_layer_norm(const Tensor &x, const OptTensor &weight, const OptTensor
 }
 
 // The layer loop of an inference forward as ONE call (sru/modules.py:617-646 is a Python loop over the layers, each
-// of them a matrix product and a recurrence launch): per layer the gate bias is laid out for the product's epilogue,
-// U = x W (+ bias) runs on the tcgen05 GEMM, and the scan reads U (and x as the highway input when k = 3) and writes
-// h in the storage type and the layer's final state in float32.  For stacks of plain layers (no layer norm, no
-// factorised projection, no custom module, identity activation) on 16-bit inputs whose shapes the GEMM takes
-// (rows, input width and D*k multiples of 8); the Python module checks that and otherwise keeps its own loop.
-// Same kernels with the same arguments as that loop: identical results.
+// of them a matrix product and a recurrence launch, with a layer norm before or after when the stack has one): per
+// layer the optional pre-norm (written in the compute type), the gate bias laid out for the product's epilogue,
+// U = x W (+ bias) on the tcgen05 GEMM, the scan (U, and x as the highway input when k = 3; h in the compute type, the
+// layer's final state in float32) and the optional post-norm.  For stacks of plain layers (no factorised projection,
+// no custom module, identity activation) whose shapes the kernels take (rows, input width and D*k multiples of 8,
+// normalised rows of at most 4096 elements); the Python module checks that and otherwise keeps its own loop.
+// x is float32 (autocast: the first layer norm then reads the unrounded rows, as the module's does) or already
+// in the compute type.  ln_weight[i] / ln_bias[i] with no elements mean "no affine part"; has_norm[i] says whether
+// layer i has a norm at all.  Same kernels with the same arguments as the Python loop: identical results.
+Tensor stack_layer_norm(const Tensor &t, const Tensor &w, const Tensor &b, double eps, at::ScalarType out, void *stream) {
+    const int64_t n = t.size(-1);
+    Tensor tc = t.contiguous();
+    Tensor y = at::empty(tc.sizes(), tc.options().dtype(out));
+    Tensor wf, bf;
+    if (w.numel() > 0) wf = w.to(at::kFloat).contiguous();
+    if (b.numel() > 0) bf = b.to(at::kFloat).contiguous();
+    const int rc = sru_b200_layer_norm_forward(y.data_ptr(), nullptr, nullptr, tc.data_ptr(),
+                                               wf.defined() ? wf.data_ptr<float>() : nullptr,
+                                               bf.defined() ? bf.data_ptr<float>() : nullptr, tc.numel() / n, n, eps,
+                                               dtype_code(tc.scalar_type()), dtype_code(out), stream);
+    TORCH_CHECK(rc == 0, "sru_b200::stack_forward: ", sru_b200_last_error());
+    return y;
+}
+
 std::vector<Tensor> b200_stack_forward(const Tensor &x, std::vector<Tensor> weights, std::vector<Tensor> weight_c,
                                        std::vector<Tensor> bias, std::vector<double> scale_x, const OptTensor &c0,
                                        const OptTensor &mask_pad, int64_t hidden, bool bidirectional,
-                                       std::vector<int64_t> ks, std::vector<int64_t> skips) {
+                                       std::vector<int64_t> ks, std::vector<int64_t> skips, bool half_is_fp16,
+                                       std::vector<int64_t> has_norm, std::vector<Tensor> ln_weight,
+                                       std::vector<Tensor> ln_bias, std::vector<double> ln_eps, bool normalize_after) {
     TORCH_CHECK(x.is_cuda() && x.dim() == 3, "sru_b200::stack_forward: x must be a CUDA tensor (length, batch, width)");
-    const auto st = x.scalar_type();
-    TORCH_CHECK(st == at::kHalf || st == at::kBFloat16, "sru_b200::stack_forward: 16-bit input expected");
+    const at::ScalarType st = half_is_fp16 ? at::kHalf : at::kBFloat16;
+    TORCH_CHECK(x.scalar_type() == st || x.scalar_type() == at::kFloat,
+                "sru_b200::stack_forward: x must be float32 or of the compute type");
     const size_t n = weights.size();
     TORCH_CHECK(n > 0 && weight_c.size() == n && bias.size() == n && scale_x.size() == n && ks.size() == n &&
-                skips.size() == n, "sru_b200::stack_forward: one entry per layer expected in every list");
+                skips.size() == n && has_norm.size() == n && ln_weight.size() == n && ln_bias.size() == n &&
+                ln_eps.size() == n, "sru_b200::stack_forward: one entry per layer expected in every list");
     c10::cuda::CUDAGuard guard(x.device());
     void *stream = at::cuda::getCurrentCUDAStream().stream();
     const int dirs = bidirectional ? 2 : 1;
@@ -258,6 +280,7 @@ std::vector<Tensor> b200_stack_forward(const Tensor &x, std::vector<Tensor> weig
     TORCH_CHECK(M > 0 && M % 8 == 0, "sru_b200::stack_forward: length * batch must be a positive multiple of 8");
     const int code = dtype_code(st);
     const auto f32 = x.options().dtype(at::kFloat);
+    const auto o16 = x.options().dtype(st);
     Tensor pad;
     if (mask_pad.has_value()) {
         pad = mask_pad.value().to(at::kBool).contiguous();
@@ -270,7 +293,7 @@ std::vector<Tensor> b200_stack_forward(const Tensor &x, std::vector<Tensor> weig
                     "sru_b200::stack_forward: c0 must be (layers, batch, width)");
     }
     Tensor c_stack = at::empty({(int64_t)n, B, D}, f32);
-    Tensor cur = x.contiguous();
+    Tensor cur = x.contiguous();       // float32 only before the first layer
     for (size_t i = 0; i < n; ++i) {
         const int64_t in = cur.size(2), k = ks[i], N = D * k, skip = skips[i];
         TORCH_CHECK(weights[i].dim() == 2 && weights[i].size(0) == in && weights[i].size(1) == N,
@@ -282,22 +305,28 @@ std::vector<Tensor> b200_stack_forward(const Tensor &x, std::vector<Tensor> weig
         Tensor wc = weight_c[i].to(at::kFloat).contiguous();
         Tensor b = bias[i].to(at::kFloat).contiguous();
         TORCH_CHECK(wc.numel() == 2 * D && b.numel() == 2 * D, "sru_b200::stack_forward: weight_c and bias hold 2 * width values");
+        // operand of the product: the normalised rows, or the input in the compute type
+        Tensor a_in;
+        if (has_norm[i] && !normalize_after) a_in = stack_layer_norm(cur, ln_weight[i], ln_bias[i], ln_eps[i], st, stream);
+        else a_in = (cur.scalar_type() == st) ? cur : cur.to(st);
         Tensor col_bias = at::empty({N}, f32);
         int rc = sru_b200_gate_bias_columns(col_bias.data_ptr<float>(), b.data_ptr<float>(), D, (int)k, stream);
         TORCH_CHECK(rc == 0, "sru_b200::stack_forward: ", sru_b200_last_error());
-        Tensor u = at::empty({M, N}, cur.options());
+        Tensor u = at::empty({M, N}, o16);
         const size_t wbytes = sru_b200_gemm_workspace_bytes(M, N, in, 1);
         Tensor ws = at::empty({(int64_t)std::max<size_t>(wbytes, 16)}, x.options().dtype(at::kByte));
-        rc = sru_b200_gemm_ws(u.data_ptr(), cur.data_ptr(), w.data_ptr(), col_bias.data_ptr<float>(), M, N, in, in, N, N,
+        rc = sru_b200_gemm_ws(u.data_ptr(), a_in.data_ptr(), w.data_ptr(), col_bias.data_ptr<float>(), M, N, in, in, N, N,
                               0, 0, code, code, 0, ws.data_ptr(), wbytes, stream);
         TORCH_CHECK(rc == 0, "sru_b200::stack_forward: ", sru_b200_last_error());
-        Tensor h = at::empty({L, B, D}, cur.options());
-        rc = sru_b200_scan_forward(h.data_ptr(), nullptr, c_stack[i].data_ptr(), u.data_ptr(),
-                                   skip == 1 ? cur.data_ptr() : nullptr, wc.data_ptr(), nullptr,
-                                   init.defined() ? init[i].data_ptr() : nullptr, nullptr,
+        Tensor hx;                      // the highway input: the layer's (un-normalised) input in the compute type
+        if (skip == 1) hx = (cur.scalar_type() == st) ? cur : cur.to(st);
+        Tensor h = at::empty({L, B, D}, o16);
+        rc = sru_b200_scan_forward(h.data_ptr(), nullptr, c_stack[i].data_ptr(), u.data_ptr(), ptr(hx), wc.data_ptr(),
+                                   nullptr, init.defined() ? init[i].data_ptr() : nullptr, nullptr,
                                    static_cast<const uint8_t *>(ptr(pad)), L, B, hidden, dirs, (int)k, 0, (int)skip, 0,
                                    scale_x[i], code, SRU_F32, stream);
         TORCH_CHECK(rc == 0, "sru_b200::stack_forward: ", sru_b200_last_error());
+        if (has_norm[i] && normalize_after) h = stack_layer_norm(h, ln_weight[i], ln_bias[i], ln_eps[i], st, stream);
         cur = h;
     }
     return {cur, c_stack};
@@ -307,7 +336,8 @@ std::vector<Tensor> b200_stack_forward(const Tensor &x, std::vector<Tensor> weig
 
 TORCH_LIBRARY(sru_b200, m) {
     m.def("stack_forward(Tensor x, Tensor[] weights, Tensor[] weight_c, Tensor[] bias, float[] scale_x, Tensor? c0, "
-          "Tensor? mask_pad, int hidden_size, bool bidirectional, int[] k, int[] skip_type) -> Tensor[]",
+          "Tensor? mask_pad, int hidden_size, bool bidirectional, int[] k, int[] skip_type, bool half_is_fp16, "
+          "int[] has_norm, Tensor[] ln_weight, Tensor[] ln_bias, float[] ln_eps, bool normalize_after) -> Tensor[]",
           &b200_stack_forward);
     m.def("gemm(Tensor x, Tensor w, Tensor? col_bias) -> Tensor", &b200_gemm);
     m.def("gate_bias_columns(Tensor bias, int width, int k) -> Tensor", &b200_gate_bias_columns);

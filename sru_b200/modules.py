@@ -540,8 +540,8 @@ class SRU(nn.Module):
         """Inference through ``sru_b200::stack_forward``: the whole layer loop as one native call (one Python to
         C++ transition instead of several per layer; same kernels and arguments as the loop, identical results).
         Returns None when the stack or the call is not of the plain kind that operator serves: gradients needed,
-        training mode, layer norm, factorised or custom projections, a non-identity activation, fp32 compute,
-        widths the tensor-core GEMM does not take, the per-kernel timer of the benchmark installed."""
+        training mode, factorised or custom projections, a non-identity activation, fp32 compute, widths the
+        kernels do not take, the per-kernel timer of the benchmark installed."""
         if (not _HAVE_TORCH_OPS or not _native_stack_enabled or torch.is_grad_enabled() or self.training
                 or not x.is_cuda or x.dim() != 3 or _lib.timer is not None or ops.get_amp_mode() != "native"
                 or gemm_backend() != "tcgen05" or not bias_fold_enabled()):
@@ -550,22 +550,47 @@ class SRU(nn.Module):
         if length == 0 or (length * batch) % 8 != 0:
             return None
         first = self.rnn_lst[0]
-        dt = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else (
+        autocast = torch.is_autocast_enabled("cuda")
+        dt = torch.get_autocast_dtype("cuda") if autocast else (
             first.weight.dtype if first.weight.dtype != x.dtype else x.dtype)
         if dt not in (torch.float16, torch.bfloat16):
+            return None
+        # what the first layer reads: under autocast a float32 input stays float32 for the first layer norm (the
+        # module's own path normalises the unrounded rows); everything else enters in the compute type
+        if x.dtype not in (torch.float32, dt) or (x.dtype == torch.float32 and not autocast):
             return None
         D = self.output_size
         width = x.size(2)
         ks: List[int] = []
         skips: List[int] = []
         scales: List[float] = []
+        has_norm: List[int] = []
+        ln_w: List[Tensor] = []
+        ln_b: List[Tensor] = []
+        ln_eps: List[float] = []
+        none = x.new_empty(0)
+        normalize_after = bool(first.normalize_after)
         for cell in self.rnn_lst:
             k = cell.num_matrices
-            if (cell.layer_norm is not None or cell.weight_proj is not None or cell.custom_m is not None
+            if (cell.weight_proj is not None or cell.custom_m is not None
                     or cell.activation_type != 0 or cell.amp_recurrence_fp16 or cell.output_size != D
                     or cell.weight.size(0) != width or width % 8 != 0 or (D * k) % 8 != 0
-                    or cell.weight.dtype not in (torch.float32, dt) or not cell.weight.is_cuda):
+                    or cell.weight.dtype not in (torch.float32, dt) or not cell.weight.is_cuda
+                    or bool(cell.normalize_after) != normalize_after):
                 return None
+            ln = cell.layer_norm
+            if ln is not None:
+                rows = D if normalize_after else width
+                if tuple(ln.normalized_shape) != (rows,) or rows > 4096:
+                    return None
+                ln_w.append(none if ln.weight is None else ln.weight)
+                ln_b.append(none if ln.bias is None else ln.bias)
+                ln_eps.append(float(ln.eps))
+            else:
+                ln_w.append(none)
+                ln_b.append(none)
+                ln_eps.append(0.0)
+            has_norm.append(0 if ln is None else 1)
             ks.append(k)
             skips.append(0 if not cell.has_skip_term else (1 if k == 3 else 2))
             scales.append(ops._scale_value(cell.scale_x if cell.rescale else None))
@@ -573,9 +598,10 @@ class SRU(nn.Module):
         if c0 is not None and (c0.dim() != 3 or c0.size(0) != self.num_layers):
             return None
         out = torch.ops.sru_b200.stack_forward(
-            x if x.dtype == dt else x.to(dt), [c.weight for c in self.rnn_lst], [c.weight_c for c in self.rnn_lst],
-            [c.bias for c in self.rnn_lst], scales, c0, mask_pad, self.hidden_size, self.bidirectional, ks, skips)
-        _lib.launch_count += 3 * len(ks)      # per layer: bias layout, product, scan
+            x, [c.weight for c in self.rnn_lst], [c.weight_c for c in self.rnn_lst], [c.bias for c in self.rnn_lst],
+            scales, c0, mask_pad, self.hidden_size, self.bidirectional, ks, skips, dt == torch.float16,
+            has_norm, ln_w, ln_b, ln_eps, normalize_after)
+        _lib.launch_count += 3 * len(ks) + sum(has_norm)      # per layer: bias layout, product, scan (+ layer norm)
         return [out[0], out[1]]
 
     @torch.jit.unused

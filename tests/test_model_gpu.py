@@ -340,12 +340,15 @@ def test_scale_x_changes_take_effect():
     (dict(hidden_size=64, num_layers=3, bidirectional=True), 31, 8, 40, True, True),       # k = 4 first layer, padding
     (dict(hidden_size=128, num_layers=2, highway_bias=-2.0, rescale=True), 16, 4, 128, True, False),
     (dict(hidden_size=32, num_layers=2, has_skip_term=False), 8, 8, 32, False, True),
+    (dict(hidden_size=64, num_layers=3, bidirectional=True, layer_norm=True), 20, 8, 128, True, False),   # pre-norm
+    (dict(hidden_size=64, num_layers=2, layer_norm=True, normalize_after=True), 12, 4, 48, False, True),  # post-norm
 ])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_native_layer_loop_matches_python_loop(kwargs, L, B, in_size, use_mask, use_c0, dtype):
     """Inference through ``sru_b200::stack_forward`` (the layer loop as one native call) gives the bits of the
     Python loop over the layers: same kernels, same arguments.  Under autocast on fp32 input and on 16-bit input
-    with 16-bit weights; stacks it does not serve (layer norm, training mode) keep the Python loop."""
+    with 16-bit weights, with and without layer norms; stacks it does not serve (a factorised projection) keep
+    the Python loop."""
     from sru_b200 import _lib, modules
     SRU = _sru()
     torch.manual_seed(L + B)
@@ -381,9 +384,11 @@ def test_native_layer_loop_matches_python_loop(kwargs, L, B, in_size, use_mask, 
         _lib.check_device_error()
         assert h1.dtype == h0.dtype and c1.dtype == c0_.dtype and h1.shape == h0.shape and c1.shape == c0_.shape
         assert torch.equal(h1, h0) and torch.equal(c1, c0_)
-        assert n1 == n0 == 3 * model.num_layers          # bias layout, product, scan per layer on both paths
+        norms = model.num_layers if kwargs.get("layer_norm") else 0
+        assert n1 == n0 == 3 * model.num_layers + norms   # bias layout, product, scan (+ norm) per layer on both paths
     # not served: falls back to the Python loop and still works
-    ln = SRU(in_size, layer_norm=True, **kwargs).to(DEV).eval()
+    pj = SRU(in_size, projection_size=16, **kwargs).to(DEV).eval()
+    n0 = _lib.launch_count
     with torch.no_grad(), torch.autocast("cuda", dtype=dtype):
-        h, c = ln(x, mask_pad=mask)
-    assert torch.isfinite(h).all()
+        h, c = pj(x, mask_pad=mask)
+    assert torch.isfinite(h.float()).all() and _lib.launch_count - n0 > 3 * pj.num_layers
