@@ -583,6 +583,8 @@ def main():
                    "parallelism": "batch-sharded dp%d" % world, "l2": "inputs larger than L2",
                    "gemm": gemm_backend(), "c_hist": ops._c_hist_dtype, "amp_mode": ops.get_amp_mode(),
                    "cuda_graph": graph is not None, "bias_in_gemm_epilogue": not args.no_bias_fold,
+                   "inference_path": None if cfg["train"] else
+                   "layer loop as one native call; the 16-bit copy of the weights and the bias layout are kept between calls",
                    "all_reduce": None if reducer is None else {
                        "dtype": args.reduce_dtype, "bytes_per_step": reducer.bytes_per_step(),
                        "start": "at bucket completion" if args.no_defer else "behind the next backward scan",

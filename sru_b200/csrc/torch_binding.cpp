@@ -242,7 +242,9 @@ Tensor b200_layer_norm(const Tensor &x, const OptTensor &weight, const OptTensor
 // no custom module, identity activation) whose shapes the kernels take (rows, input width and D*k multiples of 8,
 // normalised rows of at most 4096 elements); the Python module checks that and otherwise keeps its own loop.
 // x is float32 (autocast: the first layer norm then reads the unrounded rows, as the module's does) or already
-// in the compute type.  ln_weight[i] / ln_bias[i] with no elements mean "no affine part"; has_norm[i] says whether
+// in the compute type.  weights[i] may already be in the compute type and col_bias[i] may hold the gate bias laid out
+// over U's columns (a caller that serves many requests keeps both between calls; with no elements it is laid out
+// here).  ln_weight[i] / ln_bias[i] with no elements mean "no affine part"; has_norm[i] says whether
 // layer i has a norm at all.  Same kernels with the same arguments as the Python loop: identical results.
 Tensor stack_layer_norm(const Tensor &t, const Tensor &w, const Tensor &b, double eps, at::ScalarType out, void *stream) {
     const int64_t n = t.size(-1);
@@ -264,7 +266,8 @@ std::vector<Tensor> b200_stack_forward(const Tensor &x, std::vector<Tensor> weig
                                        const OptTensor &mask_pad, int64_t hidden, bool bidirectional,
                                        std::vector<int64_t> ks, std::vector<int64_t> skips, bool half_is_fp16,
                                        std::vector<int64_t> has_norm, std::vector<Tensor> ln_weight,
-                                       std::vector<Tensor> ln_bias, std::vector<double> ln_eps, bool normalize_after) {
+                                       std::vector<Tensor> ln_bias, std::vector<double> ln_eps, bool normalize_after,
+                                       std::vector<Tensor> col_biases) {
     TORCH_CHECK(x.is_cuda() && x.dim() == 3, "sru_b200::stack_forward: x must be a CUDA tensor (length, batch, width)");
     const at::ScalarType st = half_is_fp16 ? at::kHalf : at::kBFloat16;
     TORCH_CHECK(x.scalar_type() == st || x.scalar_type() == at::kFloat,
@@ -272,7 +275,8 @@ std::vector<Tensor> b200_stack_forward(const Tensor &x, std::vector<Tensor> weig
     const size_t n = weights.size();
     TORCH_CHECK(n > 0 && weight_c.size() == n && bias.size() == n && scale_x.size() == n && ks.size() == n &&
                 skips.size() == n && has_norm.size() == n && ln_weight.size() == n && ln_bias.size() == n &&
-                ln_eps.size() == n, "sru_b200::stack_forward: one entry per layer expected in every list");
+                ln_eps.size() == n && col_biases.size() == n,
+                "sru_b200::stack_forward: one entry per layer expected in every list");
     c10::cuda::CUDAGuard guard(x.device());
     void *stream = at::cuda::getCurrentCUDAStream().stream();
     const int dirs = bidirectional ? 2 : 1;
@@ -309,9 +313,17 @@ std::vector<Tensor> b200_stack_forward(const Tensor &x, std::vector<Tensor> weig
         Tensor a_in;
         if (has_norm[i] && !normalize_after) a_in = stack_layer_norm(cur, ln_weight[i], ln_bias[i], ln_eps[i], st, stream);
         else a_in = (cur.scalar_type() == st) ? cur : cur.to(st);
-        Tensor col_bias = at::empty({N}, f32);
-        int rc = sru_b200_gate_bias_columns(col_bias.data_ptr<float>(), b.data_ptr<float>(), D, (int)k, stream);
-        TORCH_CHECK(rc == 0, "sru_b200::stack_forward: ", sru_b200_last_error());
+        // the gate bias over U's columns: handed in by a caller that keeps it between calls, else laid out here
+        Tensor col_bias = col_biases[i];
+        int rc = 0;
+        if (col_bias.numel() == 0) {
+            col_bias = at::empty({N}, f32);
+            rc = sru_b200_gate_bias_columns(col_bias.data_ptr<float>(), b.data_ptr<float>(), D, (int)k, stream);
+            TORCH_CHECK(rc == 0, "sru_b200::stack_forward: ", sru_b200_last_error());
+        } else {
+            TORCH_CHECK(col_bias.is_cuda() && col_bias.scalar_type() == at::kFloat && col_bias.numel() == N &&
+                        col_bias.is_contiguous(), "sru_b200::stack_forward: col_bias of layer ", i, " must be float[", N, "]");
+        }
         Tensor u = at::empty({M, N}, o16);
         const size_t wbytes = sru_b200_gemm_workspace_bytes(M, N, in, 1);
         Tensor ws = at::empty({(int64_t)std::max<size_t>(wbytes, 16)}, x.options().dtype(at::kByte));
@@ -337,7 +349,8 @@ std::vector<Tensor> b200_stack_forward(const Tensor &x, std::vector<Tensor> weig
 TORCH_LIBRARY(sru_b200, m) {
     m.def("stack_forward(Tensor x, Tensor[] weights, Tensor[] weight_c, Tensor[] bias, float[] scale_x, Tensor? c0, "
           "Tensor? mask_pad, int hidden_size, bool bidirectional, int[] k, int[] skip_type, bool half_is_fp16, "
-          "int[] has_norm, Tensor[] ln_weight, Tensor[] ln_bias, float[] ln_eps, bool normalize_after) -> Tensor[]",
+          "int[] has_norm, Tensor[] ln_weight, Tensor[] ln_bias, float[] ln_eps, bool normalize_after, Tensor[] col_bias) "
+          "-> Tensor[]",
           &b200_stack_forward);
     m.def("gemm(Tensor x, Tensor w, Tensor? col_bias) -> Tensor", &b200_gemm);
     m.def("gate_bias_columns(Tensor bias, int width, int k) -> Tensor", &b200_gate_bias_columns);

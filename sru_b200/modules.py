@@ -174,6 +174,7 @@ class SRUCell(nn.Module):
             self.bias[D:].fill_(hb)
             self.scale_x[0] = highway_scale if (self.rescale and self.has_skip_term) else 1.0
             ops.forget_scale(self.scale_x)
+            self.__dict__.pop("_inference_operands", None)
 
             gates = None
             if self.custom_m is None:
@@ -215,6 +216,15 @@ class SRUCell(nn.Module):
     def _load_from_state_dict(self, *args, **kwargs):
         super()._load_from_state_dict(*args, **kwargs)
         ops.forget_scale(self.scale_x)
+        self.__dict__.pop("_inference_operands", None)
+
+    def train(self, mode: bool = True):
+        self.__dict__.pop("_inference_operands", None)     # copies kept by the native inference loop
+        return super().train(mode)
+
+    def _apply(self, fn, *args, **kwargs):
+        self.__dict__.pop("_inference_operands", None)     # .to() / .cuda() / .half() replace the parameters
+        return super()._apply(fn, *args, **kwargs)
 
     def forward(self, input: Tensor, c0: Optional[Tensor] = None,
                 mask_pad: Optional[Tensor] = None) -> Tuple[Tensor, Tensor]:
@@ -569,6 +579,8 @@ class SRU(nn.Module):
         ln_b: List[Tensor] = []
         ln_eps: List[float] = []
         none = x.new_empty(0)
+        w_list: List[Tensor] = []
+        cb_list: List[Tensor] = []
         normalize_after = bool(first.normalize_after)
         for cell in self.rnn_lst:
             k = cell.num_matrices
@@ -591,6 +603,17 @@ class SRU(nn.Module):
                 ln_b.append(none)
                 ln_eps.append(0.0)
             has_norm.append(0 if ln is None else 1)
+            # the weight in the compute type and the gate bias laid out over U's columns are kept between calls
+            # (inference weights do not change; the key follows in-place updates autograd can see, and
+            # reset_parameters / load_state_dict / train() drop the copies)
+            key = (cell.weight.data_ptr(), cell.weight._version, cell.bias.data_ptr(), cell.bias._version, dt)
+            kept = cell.__dict__.get("_inference_operands")
+            if kept is None or kept[0] != key:
+                w16 = cell.weight.detach() if cell.weight.dtype == dt else cell.weight.detach().to(dt)
+                kept = (key, w16.contiguous(), gate_bias_columns(cell.bias.detach(), D, k))
+                cell.__dict__["_inference_operands"] = kept
+            w_list.append(kept[1])
+            cb_list.append(kept[2])
             ks.append(k)
             skips.append(0 if not cell.has_skip_term else (1 if k == 3 else 2))
             scales.append(ops._scale_value(cell.scale_x if cell.rescale else None))
@@ -598,10 +621,10 @@ class SRU(nn.Module):
         if c0 is not None and (c0.dim() != 3 or c0.size(0) != self.num_layers):
             return None
         out = torch.ops.sru_b200.stack_forward(
-            x, [c.weight for c in self.rnn_lst], [c.weight_c for c in self.rnn_lst], [c.bias for c in self.rnn_lst],
+            x, w_list, [c.weight_c for c in self.rnn_lst], [c.bias for c in self.rnn_lst],
             scales, c0, mask_pad, self.hidden_size, self.bidirectional, ks, skips, dt == torch.float16,
-            has_norm, ln_w, ln_b, ln_eps, normalize_after)
-        _lib.launch_count += 3 * len(ks) + sum(has_norm)      # per layer: bias layout, product, scan (+ layer norm)
+            has_norm, ln_w, ln_b, ln_eps, normalize_after, cb_list)
+        _lib.launch_count += 2 * len(ks) + sum(has_norm)      # per layer: product, scan (+ layer norm)
         return [out[0], out[1]]
 
     @torch.jit.unused

@@ -385,7 +385,15 @@ def test_native_layer_loop_matches_python_loop(kwargs, L, B, in_size, use_mask, 
         assert h1.dtype == h0.dtype and c1.dtype == c0_.dtype and h1.shape == h0.shape and c1.shape == c0_.shape
         assert torch.equal(h1, h0) and torch.equal(c1, c0_)
         norms = model.num_layers if kwargs.get("layer_norm") else 0
-        assert n1 == n0 == 3 * model.num_layers + norms   # bias layout, product, scan (+ norm) per layer on both paths
+        assert n0 == 3 * model.num_layers + norms          # Python loop: bias layout, product, scan (+ norm) per layer
+        assert n1 in (n0, n0 - model.num_layers)           # native loop: the bias layout is kept between calls
+    # the copies kept between calls follow in-place updates of the parameters
+    with torch.no_grad():
+        model.rnn_lst[0].weight.mul_(0.5)
+        model.rnn_lst[-1].bias.add_(0.25)
+    ha, ca, _ = run(True, True)
+    hb, cb, _ = run(False, True)
+    assert torch.equal(ha, hb) and torch.equal(ca, cb) and not torch.equal(ha, h1)
     # not served: falls back to the Python loop and still works
     pj = SRU(in_size, projection_size=16, **kwargs).to(DEV).eval()
     n0 = _lib.launch_count
