@@ -221,17 +221,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-// The same wait, naming the registers an earlier tcgen05.ld fills: their readers cannot be scheduled above it.
-__device__ __forceinline__ void tmem_ld_wait_for(uint32_t (&r)[32]) {
-    asm volatile("tcgen05.wait::ld.sync.aligned;"
-                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
-                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
-                   "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
-                   "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
-                 :
-                 : "memory");
-}
-
 // Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
 __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
     uint64_t d = 0;
@@ -524,7 +513,7 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t adesc, uin
 // 128 bytes in the 128-byte swizzle of the map (chunk j of row r at chunk j ^ (r & 7): conflict-free for the row-wise
 // writes as well) and one lane hands both boxes to the TMA engine, which also clips rows beyond M and columns beyond N.
 // The warp goes straight back to the accumulator; before it writes the buffer again it waits until the engine has read it.
-template <typename TO, bool AHEAD>
+template <typename TO>
 __device__ __forceinline__ void epilogue_staged(const GemmArgs &g, uint32_t tmem_warp, int64_t row0, int64_t col_base,
                                                 uint8_t *stg, int lane, int h, const CUtensorMap *map_c) {
     const int64_t row = row0 + lane;
@@ -567,43 +556,20 @@ __device__ __forceinline__ void epilogue_staged(const GemmArgs &g, uint32_t tmem
                     store8<TO>(reinterpret_cast<TO *>(stg + lane * kStgRow + ((chunk ^ (lane & 15)) << 4)), v);
             }
         };
-        if constexpr (AHEAD) {
-            // The accumulator chunks are requested one ahead: chunk c + 1 travels from tensor memory while chunk c is
-            // converted and staged (two register sets; the loop is unrolled so that their indices are constants).
-            // For the instance with four epilogue warps (long reductions: 5 % on the 256 000 x 6144 x 2048 product);
-            // the eight-warp instance has 200 registers per thread and spills with two sets (measured: 30 % slower).
-            uint32_t r[2][32];
-            tmem_ld32(tmem_warp + h * 128, r[0]);
-            if (map_c) {
-                if (lane == 0) bulk_wait_read_all();
-                __syncwarp();
-            }
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const int64_t col0 = colh + c * 32;
-                if (col0 >= g.N) break;
-                float4 bv[8];
-                load_bias(col0, bv);
-                tmem_ld_wait_for(r[c & 1]);
-                if (c < 3 && col0 + 32 < g.N) tmem_ld32(tmem_warp + h * 128 + (c + 1) * 32, r[(c + 1) & 1]);
-                stage_chunk(c, col0, r[c & 1], bv);
-            }
-        } else {
-            if (map_c) {
-                if (lane == 0) bulk_wait_read_all();
-                __syncwarp();
-            }
+        if (map_c) {
+            if (lane == 0) bulk_wait_read_all();
+            __syncwarp();
+        }
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                const int64_t col0 = colh + c * 32;
-                if (col0 >= g.N) break;
-                float4 bv[8];
-                load_bias(col0, bv);
-                uint32_t r[32];
-                tmem_ld32(tmem_warp + h * 128 + c * 32, r);
-                tmem_ld_wait();
-                stage_chunk(c, col0, r, bv);
-            }
+        for (int c = 0; c < 4; ++c) {
+            const int64_t col0 = colh + c * 32;
+            if (col0 >= g.N) break;
+            float4 bv[8];
+            load_bias(col0, bv);
+            uint32_t r[32];
+            tmem_ld32(tmem_warp + h * 128 + c * 32, r);
+            tmem_ld_wait();
+            stage_chunk(c, col0, r, bv);
         }
         if (map_c) {
             fence_proxy_async();      // the generic-proxy writes above become visible to the bulk copy engine
@@ -798,10 +764,10 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             const uint32_t tmem_warp = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
             if (g.c_dtype == SRU_BF16) {
                 for (int h = h_first; h <= h_last; ++h)
-                    epilogue_staged<__nv_bfloat16, EW == 4>(g, tmem_warp, row0, col_base, stg, lane, h, g.c_tma ? &map_c : nullptr);
+                    epilogue_staged<__nv_bfloat16>(g, tmem_warp, row0, col_base, stg, lane, h, g.c_tma ? &map_c : nullptr);
             } else if (g.c_dtype == SRU_F16) {
                 for (int h = h_first; h <= h_last; ++h)
-                    epilogue_staged<__half, EW == 4>(g, tmem_warp, row0, col_base, stg, lane, h, g.c_tma ? &map_c : nullptr);
+                    epilogue_staged<__half>(g, tmem_warp, row0, col_base, stg, lane, h, g.c_tma ? &map_c : nullptr);
             } else {
 #pragma unroll 1
                 for (int c = h_first * 4; c < h_last * 4 + 4; ++c) {

@@ -606,9 +606,12 @@ class SRU(nn.Module):
             # the weight in the compute type and the gate bias laid out over U's columns are kept between calls
             # (inference weights do not change; the key follows in-place updates autograd can see, and
             # reset_parameters / load_state_dict / train() drop the copies)
-            key = (cell.weight.data_ptr(), cell.weight._version, cell.bias.data_ptr(), cell.bias._version, dt)
+            try:
+                key = (cell.weight.data_ptr(), cell.weight._version, cell.bias.data_ptr(), cell.bias._version, dt)
+            except RuntimeError:        # parameters made in inference mode track no version: nothing is kept
+                key = None
             kept = cell.__dict__.get("_inference_operands")
-            if kept is None or kept[0] != key:
+            if key is None or kept is None or kept[0] != key:
                 w16 = cell.weight.detach() if cell.weight.dtype == dt else cell.weight.detach().to(dt)
                 kept = (key, w16.contiguous(), gate_bias_columns(cell.bias.detach(), D, k))
                 cell.__dict__["_inference_operands"] = kept
