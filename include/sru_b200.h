@@ -226,6 +226,14 @@ int sru_b200_gemm(
 int sru_b200_gate_bias_columns(float *col_bias, const float *bias, int64_t width, int k, void *stream);
 
 /*
+ * dst[i] = (dst type) src[i] for n elements, between float32 and one of the 16-bit types (either direction; round to
+ * nearest even when narrowing).  Pointers 16-byte aligned.  Stands in for the framework's converting copy where the
+ * module widens the last layer's 16-bit h to the float32 the reference returns (sru/ops.py:116-127) and narrows its
+ * gradient; no counterpart in the reference's extension.
+ */
+int sru_b200_convert(void *dst, const void *src, int64_t n, int src_dtype, int dst_dtype, void *stream);
+
+/*
  * The same contraction with caller-provided scratch.  Products whose output tiles alone
  * cannot fill the GPU but whose reduction is long (the weight gradient x^T grad_U:
  * M = input width, K = length * batch) are cut into K slabs whose fp32 partial results go to

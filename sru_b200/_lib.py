@@ -58,6 +58,8 @@ def lib():
         l.sru_b200_gemm.argtypes = [_vp] * 4 + [_i64] * 6 + [_int] * 5 + [_vp]
         l.sru_b200_gate_bias_columns.restype = _int
         l.sru_b200_gate_bias_columns.argtypes = [_vp, _vp, _i64, _int, _vp]
+        l.sru_b200_convert.restype = _int
+        l.sru_b200_convert.argtypes = [_vp, _vp, _i64, _int, _int, _vp]
         l.sru_b200_gemm_workspace_bytes.restype = ctypes.c_size_t
         l.sru_b200_gemm_workspace_bytes.argtypes = [_i64, _i64, _i64, _int]
         l.sru_b200_gemm_ws.restype = _int

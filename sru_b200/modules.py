@@ -240,7 +240,7 @@ class SRUCell(nn.Module):
     def _restore_output_dtype(self, h: Tensor, input: Tensor) -> Tensor:
         if ops.get_amp_mode() == "native" and h.dtype in (torch.float16, torch.bfloat16) \
                 and input.dtype == torch.float32 and not self.amp_recurrence_fp16:
-            return h.float()
+            return ops.widen_to_float32(h)
         return h
 
     def forward_native(self, input: Tensor, c0: Optional[Tensor] = None,
@@ -655,7 +655,7 @@ class SRU(nn.Module):
         reference would return (float32 under autocast, see sru/ops.py:116-127)."""
         if ops.get_amp_mode() == "native" and h.dtype in (torch.float16, torch.bfloat16) \
                 and input.dtype == torch.float32 and not self.amp_recurrence_fp16:
-            return h.float()
+            return ops.widen_to_float32(h)
         return h
 
     def reset_parameters(self):

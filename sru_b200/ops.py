@@ -184,6 +184,44 @@ def _scale_value(scale_x: Optional[Tensor]) -> float:
     return value
 
 
+def _convert(t: Tensor, dtype: torch.dtype) -> Tensor:
+    """t in ``dtype`` through ``sru_b200_convert`` (float32 <-> fp16 / bf16, contiguous CUDA tensors)."""
+    out = torch.empty(t.shape, dtype=dtype, device=t.device)
+    if t.numel():
+        with torch.cuda.device(t.device):
+            _lib.call("convert", 1 if t.numel() % 8 == 0 else 2, _lib.lib().sru_b200_convert, _lib.ptr(out), _lib.ptr(t),
+                      t.numel(), _lib.DTYPE_CODE[t.dtype], _lib.DTYPE_CODE[dtype], _lib.current_stream_ptr(t.device))
+    return out
+
+
+class _Widen(torch.autograd.Function):
+    """16-bit -> float32 with the adjoint float32 -> 16-bit, both on this package's conversion kernel."""
+
+    @staticmethod
+    def forward(ctx, t):
+        ctx.src_dtype = t.dtype
+        return _convert(t, torch.float32)
+
+    @staticmethod
+    def backward(ctx, grad):
+        g = grad if grad.is_contiguous() else grad.contiguous()
+        if g.dtype != torch.float32:
+            return g.to(ctx.src_dtype)
+        return _convert(g, ctx.src_dtype)
+
+
+def widen_to_float32(t: Tensor) -> Tensor:
+    """``t.float()`` for the 16-bit h the module hands back as float32 (the reference's return type under 16-bit
+    autocast, sru/ops.py:116-127).  The framework's converting copy of a large tensor runs at about a quarter of the HBM
+    bandwidth; this one is bound by it.  Anything the kernel does not take (CPU, non-contiguous, unaligned, other
+    types) is converted by the framework."""
+    if (t.is_cuda and t.dtype in (torch.float16, torch.bfloat16) and t.is_contiguous() and t.data_ptr() % 16 == 0
+            and not torch.jit.is_scripting()):
+        with torch.autocast("cuda", enabled=False):
+            return _Widen.apply(t)
+    return t.float()
+
+
 def forget_scale(scale_x: Optional[Tensor]) -> None:
     """Drops the remembered scalar of ``scale_x`` (call after writing to it through ``.data``)."""
     if scale_x is not None and hasattr(scale_x, "_sru_b200_scalar"):

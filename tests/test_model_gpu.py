@@ -385,7 +385,8 @@ def test_native_layer_loop_matches_python_loop(kwargs, L, B, in_size, use_mask, 
         assert h1.dtype == h0.dtype and c1.dtype == c0_.dtype and h1.shape == h0.shape and c1.shape == c0_.shape
         assert torch.equal(h1, h0) and torch.equal(c1, c0_)
         norms = model.num_layers if kwargs.get("layer_norm") else 0
-        assert n0 == 3 * model.num_layers + norms          # Python loop: bias layout, product, scan (+ norm) per layer
+        widen = 1 if autocast else 0                       # float32 input under autocast: h comes back as float32
+        assert n0 == 3 * model.num_layers + norms + widen  # Python loop: bias layout, product, scan (+ norm) per layer
         assert n1 in (n0, n0 - model.num_layers)           # native loop: the bias layout is kept between calls
     # the copies kept between calls follow in-place updates of the parameters
     with torch.no_grad():
@@ -400,3 +401,29 @@ def test_native_layer_loop_matches_python_loop(kwargs, L, B, in_size, use_mask, 
     with torch.no_grad(), torch.autocast("cuda", dtype=dtype):
         h, c = pj(x, mask_pad=mask)
     assert torch.isfinite(h.float()).all() and _lib.launch_count - n0 > 3 * pj.num_layers
+
+
+@pytest.mark.parametrize("n", [8, 13, 4096 + 3, 1 << 20])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_widening_cast_matches_the_framework(n, dtype):
+    """The conversion kernel behind the module's float32 output: the bits of ``Tensor.float()`` going up and of
+    ``Tensor.to(dtype)`` (round to nearest even, infinities, NaN-ness) coming back as the gradient."""
+    from sru_b200 import _lib, ops
+    g = torch.Generator().manual_seed(n)
+    t = (torch.randn(n, generator=g) * 50).to(dtype).to(DEV)
+    t[:3] = torch.tensor([float("inf"), -0.0, 65504.0 if dtype == torch.float16 else 3.3e38], dtype=dtype)
+    leaf = t.clone().requires_grad_(True)
+    up = ops.widen_to_float32(leaf)
+    assert up.dtype == torch.float32 and torch.equal(up, t.float())
+    grad = torch.randn(n, generator=g).to(DEV) * 1e3
+    grad[:2] = torch.tensor([float("nan"), 1e39], device=DEV)
+    up.backward(grad)
+    want = grad.to(dtype)
+    assert leaf.grad.dtype == dtype
+    assert torch.equal(torch.isnan(leaf.grad), torch.isnan(want))
+    assert torch.equal(torch.nan_to_num(leaf.grad.float()), torch.nan_to_num(want.float()))
+    # what the kernel does not take goes to the framework
+    view = t.view(-1)[1:] if n > 8 else t[::2]
+    assert torch.equal(ops.widen_to_float32(view), view.float())
+    torch.cuda.synchronize()
+    _lib.check_device_error()
