@@ -427,3 +427,23 @@ def test_widening_cast_matches_the_framework(n, dtype):
     assert torch.equal(ops.widen_to_float32(view), view.float())
     torch.cuda.synchronize()
     _lib.check_device_error()
+
+
+def test_streaming_chunks_equal_one_pass():
+    """``StreamingSRU``: a unidirectional stack fed in chunks (state handed on) gives the bits of one pass over the
+    whole sequence, for chunks whose projection runs on the same GEMM; bidirectional stacks are refused."""
+    from sru_b200.streaming import StreamingSRU
+    SRU = _sru()
+    torch.manual_seed(5)
+    model = SRU(64, 64, num_layers=3, layer_norm=True).to(DEV).eval()
+    L, B = 96, 8
+    x = torch.randn(L, B, 64, device=DEV)
+    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+        h_all, c_all = model(x)
+        stream = StreamingSRU(model)
+        parts = [stream.step(x[a:b]) for a, b in ((0, 16), (16, 17), (17, 64), (64, 96))]
+    assert torch.equal(torch.cat(parts, 0), h_all) and torch.equal(stream.state, c_all)
+    stream.reset()
+    assert stream.state is None
+    with pytest.raises(ValueError):
+        StreamingSRU(SRU(64, 64, bidirectional=True))
