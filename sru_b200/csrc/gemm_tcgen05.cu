@@ -254,6 +254,31 @@ template <> __device__ __forceinline__ void store8<__half>(__half *dst, const fl
     *reinterpret_cast<uint4 *>(dst) = o;
 }
 
+// Eight values of C as one 16-byte load (rows and column groups of C are 16-byte aligned: ldc and the column offsets
+// are multiples of 8 elements), unpacked to float.
+template <typename TO> struct C8 { uint4 q; };
+template <> struct C8<float> { float4 a, b; };
+template <typename TO> __device__ __forceinline__ C8<TO> load8(const TO *src) {
+    C8<TO> c;
+    c.q = *reinterpret_cast<const uint4 *>(src);
+    return c;
+}
+template <> __device__ __forceinline__ C8<float> load8<float>(const float *src) {
+    C8<float> c;
+    c.a = reinterpret_cast<const float4 *>(src)[0];
+    c.b = reinterpret_cast<const float4 *>(src)[1];
+    return c;
+}
+template <typename TO> __device__ __forceinline__ void add8(float *v, const C8<TO> &c) {
+    const TO *e = reinterpret_cast<const TO *>(&c.q);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] += Cvt<TO>::to_f(e[j]);
+}
+template <> __device__ __forceinline__ void add8<float>(float *v, const C8<float> &c) {
+    v[0] += c.a.x; v[1] += c.a.y; v[2] += c.a.z; v[3] += c.a.w;
+    v[4] += c.b.x; v[5] += c.b.y; v[6] += c.b.z; v[7] += c.b.w;
+}
+
 // Epilogue of one 32-column chunk of one row: bias, optional accumulate, convert, store.
 template <typename TO>
 __device__ __forceinline__ void epilogue_chunk(const GemmArgs &g, const uint32_t (&r)[32], int64_t row, int64_t col0) {
@@ -270,10 +295,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmArgs &g, const uint32_t
             v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
             v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
         }
-        if (g.accumulate) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] += Cvt<TO>::to_f(crow[j0 + j]);
-        }
+        if (g.accumulate) add8<TO>(v, load8<TO>(crow + j0));
         store8<TO>(crow + j0, v);
     }
 }
@@ -530,8 +552,18 @@ __device__ __forceinline__ void epilogue_staged(const GemmArgs &g, uint32_t tmem
                                                    : make_float4(0.f, 0.f, 0.f, 0.f);
             }
         };
+        // when accumulating, the chunk's values of C are requested before the wait for the accumulator as well: one
+        // 16-byte load per eight columns of this lane's row
+        auto load_c = [&](int64_t col0, C8<TO> (&cv)[4]) {
+            if (g.accumulate && row < g.M) {
+                const TO *crow = reinterpret_cast<const TO *>(g.c) + row * g.ldc + col0;
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    if (col0 + q * 8 < g.N) cv[q] = load8<TO>(crow + q * 8);
+            }
+        };
         // one chunk of 32 accumulator columns: bias, accumulate, convert, stage
-        auto stage_chunk = [&](int c, int64_t col0, const uint32_t (&r)[32], const float4 (&bv)[8]) {
+        auto stage_chunk = [&](int c, int64_t col0, const uint32_t (&r)[32], const float4 (&bv)[8], const C8<TO> (&cv)[4]) {
 #pragma unroll
             for (int j0 = 0; j0 < 32; j0 += 8) {
                 float v[8];
@@ -543,11 +575,7 @@ __device__ __forceinline__ void epilogue_staged(const GemmArgs &g, uint32_t tmem
                         v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
                         v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
                     }
-                    if (g.accumulate && row < g.M) {
-                        const TO *crow = reinterpret_cast<const TO *>(g.c) + row * g.ldc + col0 + j0;
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) v[j] += Cvt<TO>::to_f(crow[j]);
-                    }
+                    if (g.accumulate && row < g.M) add8<TO>(v, cv[j0 >> 3]);
                 }
                 const int chunk = c * 4 + (j0 >> 3);      // 16-byte chunk of this lane's 256-byte row
                 if (map_c)
@@ -566,10 +594,12 @@ __device__ __forceinline__ void epilogue_staged(const GemmArgs &g, uint32_t tmem
             if (col0 >= g.N) break;
             float4 bv[8];
             load_bias(col0, bv);
+            C8<TO> cv[4];
+            load_c(col0, cv);
             uint32_t r[32];
             tmem_ld32(tmem_warp + h * 128 + c * 32, r);
             tmem_ld_wait();
-            stage_chunk(c, col0, r, bv);
+            stage_chunk(c, col0, r, bv, cv);
         }
         if (map_c) {
             fence_proxy_async();      // the generic-proxy writes above become visible to the bulk copy engine
