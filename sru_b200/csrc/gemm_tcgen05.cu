@@ -838,13 +838,18 @@ __global__ void splitk_reduce(const float *__restrict__ ws, int nsplit, int64_t 
             const float4 v = *reinterpret_cast<const float4 *>(ws + ((int64_t)sp * M + row) * N + col);
             acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
-        TO *o = c + row * ldc + col;
+        // four elements of C as one access (ldc and col are multiples of 4 elements, C is 16-byte aligned)
+        using P4 = Pack<TO, 4>;
+        P4 *o = reinterpret_cast<P4 *>(c + row * ldc + col);
         if (accumulate) {
-            acc.x += Cvt<TO>::to_f(o[0]); acc.y += Cvt<TO>::to_f(o[1]);
-            acc.z += Cvt<TO>::to_f(o[2]); acc.w += Cvt<TO>::to_f(o[3]);
+            const P4 old = *o;
+            acc.x += Cvt<TO>::to_f(old.v[0]); acc.y += Cvt<TO>::to_f(old.v[1]);
+            acc.z += Cvt<TO>::to_f(old.v[2]); acc.w += Cvt<TO>::to_f(old.v[3]);
         }
-        o[0] = Cvt<TO>::from_f(acc.x); o[1] = Cvt<TO>::from_f(acc.y);
-        o[2] = Cvt<TO>::from_f(acc.z); o[3] = Cvt<TO>::from_f(acc.w);
+        P4 out;
+        out.v[0] = Cvt<TO>::from_f(acc.x); out.v[1] = Cvt<TO>::from_f(acc.y);
+        out.v[2] = Cvt<TO>::from_f(acc.z); out.v[3] = Cvt<TO>::from_f(acc.w);
+        *o = out;
     }
 }
 
