@@ -535,7 +535,7 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t adesc, uin
 // 128 bytes in the 128-byte swizzle of the map (chunk j of row r at chunk j ^ (r & 7): conflict-free for the row-wise
 // writes as well) and one lane hands both boxes to the TMA engine, which also clips rows beyond M and columns beyond N.
 // The warp goes straight back to the accumulator; before it writes the buffer again it waits until the engine has read it.
-template <typename TO>
+template <typename TO, bool ACC>
 __device__ __forceinline__ void epilogue_staged(const GemmArgs &g, uint32_t tmem_warp, int64_t row0, int64_t col_base,
                                                 uint8_t *stg, int lane, int h, const CUtensorMap *map_c) {
     const int64_t row = row0 + lane;
@@ -554,8 +554,8 @@ __device__ __forceinline__ void epilogue_staged(const GemmArgs &g, uint32_t tmem
         };
         // when accumulating, the chunk's values of C are requested before the wait for the accumulator as well: one
         // 16-byte load per eight columns of this lane's row
-        auto load_c = [&](int64_t col0, C8<TO> (&cv)[4]) {
-            if (g.accumulate && row < g.M) {
+        auto load_c = [&](int64_t col0, C8<TO> (&cv)[ACC ? 4 : 1]) {
+            if (ACC && row < g.M) {
                 const TO *crow = reinterpret_cast<const TO *>(g.c) + row * g.ldc + col0;
 #pragma unroll
                 for (int q = 0; q < 4; ++q)
@@ -563,7 +563,7 @@ __device__ __forceinline__ void epilogue_staged(const GemmArgs &g, uint32_t tmem
             }
         };
         // one chunk of 32 accumulator columns: bias, accumulate, convert, stage
-        auto stage_chunk = [&](int c, int64_t col0, const uint32_t (&r)[32], const float4 (&bv)[8], const C8<TO> (&cv)[4]) {
+        auto stage_chunk = [&](int c, int64_t col0, const uint32_t (&r)[32], const float4 (&bv)[8], const C8<TO> (&cv)[ACC ? 4 : 1]) {
 #pragma unroll
             for (int j0 = 0; j0 < 32; j0 += 8) {
                 float v[8];
@@ -575,7 +575,7 @@ __device__ __forceinline__ void epilogue_staged(const GemmArgs &g, uint32_t tmem
                         v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
                         v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
                     }
-                    if (g.accumulate && row < g.M) add8<TO>(v, cv[j0 >> 3]);
+                    if constexpr (ACC) { if (row < g.M) add8<TO>(v, cv[j0 >> 3]); }
                 }
                 const int chunk = c * 4 + (j0 >> 3);      // 16-byte chunk of this lane's 256-byte row
                 if (map_c)
@@ -594,8 +594,8 @@ __device__ __forceinline__ void epilogue_staged(const GemmArgs &g, uint32_t tmem
             if (col0 >= g.N) break;
             float4 bv[8];
             load_bias(col0, bv);
-            C8<TO> cv[4];
-            load_c(col0, cv);
+            C8<TO> cv[ACC ? 4 : 1];
+            if constexpr (ACC) load_c(col0, cv);
             uint32_t r[32];
             tmem_ld32(tmem_warp + h * 128 + c * 32, r);
             tmem_ld_wait();
@@ -626,7 +626,9 @@ __device__ __forceinline__ void epilogue_staged(const GemmArgs &g, uint32_t tmem
     }
 }
 
-template <int EW>     // working epilogue warps per CTA: 4 (192 threads) or 8 (320 threads)
+// EW: working epilogue warps per CTA, 4 (192 threads) or 8 (320 threads).  ACC: the 16-bit epilogue adds onto C (the
+// dgrad product); a compile-time choice so that the other products do not carry the registers of the values of C.
+template <int EW, bool ACC>
 __global__ void __launch_bounds__(64 + 32 * EW, 1)
 gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                         const __grid_constant__ CUtensorMap map_c, const GemmArgs g) {
@@ -794,10 +796,10 @@ gemm_tcgen05_2sm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
             const uint32_t tmem_warp = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
             if (g.c_dtype == SRU_BF16) {
                 for (int h = h_first; h <= h_last; ++h)
-                    epilogue_staged<__nv_bfloat16>(g, tmem_warp, row0, col_base, stg, lane, h, g.c_tma ? &map_c : nullptr);
+                    epilogue_staged<__nv_bfloat16, ACC>(g, tmem_warp, row0, col_base, stg, lane, h, g.c_tma ? &map_c : nullptr);
             } else if (g.c_dtype == SRU_F16) {
                 for (int h = h_first; h <= h_last; ++h)
-                    epilogue_staged<__half>(g, tmem_warp, row0, col_base, stg, lane, h, g.c_tma ? &map_c : nullptr);
+                    epilogue_staged<__half, ACC>(g, tmem_warp, row0, col_base, stg, lane, h, g.c_tma ? &map_c : nullptr);
             } else {
 #pragma unroll 1
                 for (int c = h_first * 4; c < h_last * 4 + 4; ++c) {
@@ -1050,9 +1052,13 @@ static int gemm_impl(void *c, const void *a, const void *b, const float *col_bia
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
         SRUB_CUDA_CHECK(cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              kSmemBytes));
-        SRUB_CUDA_CHECK(cudaFuncSetAttribute(gemm_tcgen05_2sm_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        SRUB_CUDA_CHECK(cudaFuncSetAttribute(gemm_tcgen05_2sm_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              kSmemBytes2));
-        SRUB_CUDA_CHECK(cudaFuncSetAttribute(gemm_tcgen05_2sm_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        SRUB_CUDA_CHECK(cudaFuncSetAttribute(gemm_tcgen05_2sm_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             kSmemBytes2));
+        SRUB_CUDA_CHECK(cudaFuncSetAttribute(gemm_tcgen05_2sm_kernel<8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             kSmemBytes2));
+        SRUB_CUDA_CHECK(cudaFuncSetAttribute(gemm_tcgen05_2sm_kernel<8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              kSmemBytes2));
         attr_set[dev] = true;
     }
@@ -1096,8 +1102,15 @@ static int gemm_impl(void *c, const void *a, const void *b, const float *col_bia
         attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        if (g.epi_warps == 8) SRUB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tcgen05_2sm_kernel<8>, map_a, map_b, map_c, g));
-        else SRUB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tcgen05_2sm_kernel<4>, map_a, map_b, map_c, g));
+        // the accumulating 16-bit epilogue is its own instance (fp32 output accumulates in the plain chunk epilogue)
+        const bool acc16 = g.accumulate && g.c_dtype != SRU_F32;
+        if (g.epi_warps == 8) {
+            if (acc16) SRUB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tcgen05_2sm_kernel<8, true>, map_a, map_b, map_c, g));
+            else SRUB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tcgen05_2sm_kernel<8, false>, map_a, map_b, map_c, g));
+        } else {
+            if (acc16) SRUB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tcgen05_2sm_kernel<4, true>, map_a, map_b, map_c, g));
+            else SRUB_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_tcgen05_2sm_kernel<4, false>, map_a, map_b, map_c, g));
+        }
     } else {
         const unsigned grid = (unsigned)std::min<int64_t>(ntiles, plan.workers);
         gemm_tcgen05_kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(map_a, map_b, g);
