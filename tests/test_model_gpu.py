@@ -447,3 +447,24 @@ def test_streaming_chunks_equal_one_pass():
     assert stream.state is None
     with pytest.raises(ValueError):
         StreamingSRU(SRU(64, 64, bidirectional=True))
+
+
+def test_device_prefetcher_yields_the_batches_in_order():
+    """``DevicePrefetcher``: batch i + 1 is copied on a side stream while batch i is in use; the consumer sees every
+    batch, in order, with the host values, and None entries pass through."""
+    from sru_b200.data import DevicePrefetcher
+    g = torch.Generator().manual_seed(1)
+    host = [(torch.randn(64, 8, 32, generator=g).pin_memory(), None if i % 2 else (torch.rand(64, 8, generator=g) > 0.5).pin_memory())
+            for i in range(5)]
+    seen = 0
+    acc = torch.zeros((), device=DEV)
+    for i, (x, m) in enumerate(DevicePrefetcher(iter(host), DEV)):
+        assert x.is_cuda and torch.equal(x.cpu(), host[i][0])
+        assert (m is None) == (host[i][1] is None) and (m is None or torch.equal(m.cpu(), host[i][1]))
+        acc += (x * 2).sum()          # work on the consumer's stream while the next copy runs
+        seen += 1
+    assert seen == 5
+    assert abs(float(acc) - 2 * sum(float(h[0].sum()) for h in host)) < 1e-1
+    assert list(DevicePrefetcher(iter([]), DEV)) == []
+    with pytest.raises(ValueError):
+        DevicePrefetcher(iter(host), "cpu")
